@@ -6,7 +6,7 @@ in the compute dtype or the one the spec gives (inside a page the layout is head
 (page, head) is one contiguous page_size x width tile; the reference's pool is
 [slot, kv_heads, head_dim], crates/engine/src/backend/paged.rs:25-27, and leaves the layout to
 the backend, crates/engine/src/backend/mod.rs:10-12). Calls whose mixers ask for the same kind
-of cache (all keys, or a window of w) with the same tensors form a group: one page pool and one block table per request serve all of them, a page number being
+of cache (all keys, a window of w, or blocks of w positions) with the same tensors form a group: one page pool and one block table per request serve all of them, a page number being
 valid in every layer of its group. Mixers with fixed-size state get a tensor
 [max_seqs, *shape] indexed by the request's state slot. The page bookkeeping itself is the
 native `CacheManager`.
@@ -78,9 +78,9 @@ class CachePools:
         groups = []
         for key in group_keys:
             kind, window = key[0], key[1]
-            if kind not in ("full", "window"):
-                raise ConfigError(f"cache kind {kind!r} is not known (full or window)")
-            groups.append(rt.GroupSpec(rt.WINDOW if kind == "window" else rt.FULL, int(window), self.num_pages))
+            if kind not in ("full", "window", "chunk"):
+                raise ConfigError(f"cache kind {kind!r} is not known (full, window or chunk)")
+            groups.append(rt.GroupSpec({"full": rt.FULL, "window": rt.WINDOW, "chunk": rt.CHUNK}[kind], int(window), self.num_pages))
         self.manager = rt.CacheManager(page_size, groups, max_seqs)
         # cache number -> its tensors, in the order of the spec (K, V by default)
         self.kv: Dict[int, tuple] = {}

@@ -1,13 +1,16 @@
 // Softmax attention over a paged cache whose keys and values have sizes of their own, with the
 // options a design may switch on one by one: rotary positions on part of each head, q and k brought
 // to unit root mean square, a query factor that grows with the position, values mixed with those an
-// earlier layer made of the same token, a window, a sink in the softmax, a sigmoid gate on the result.
+// earlier layer made of the same token, a window, blocks of positions, a cap on the scores, a bias that grows with the
+// distance, a sink in the softmax, a sigmoid gate on the result.
 //
 // Two steps per call of a layer:
 //   vob_flex_prep      per token: q, k, v (columns of one projection output) -> q' to a buffer, k' and
 //                      v' to their cache slots;
 //   vob_flex_attention per (row, head a), the row at position p of its request, g = a / (H / G):
-//       s_j = (q'_a . K[j, g]) * scale          for keys j in [first, p], first = max(0, p + 1 - window)
+//       s_j = (q'_a . K[j, g]) * scale          for keys j in [first, p], first = max(0, p + 1 - window), and with
+//                                                `chunk` not before p - p % chunk (the query's own block of positions)
+//       s_j <- cap * tanh(s_j / cap)  (cap > 0);   s_j <- s_j - r1_a * ln(1 + r2_a * (p - j))  (r1, r2 given)
 //       den = sum_j exp(s_j) (+ exp(sink_a): a key with no value, counted once)
 //       out_a = sum_j exp(s_j) V[j, g] / den    (* sigmoid(gate) * out_scale)
 // The step's own keys are in the cache before they are read. Scores, softmax, angles, norms and the
@@ -22,19 +25,21 @@ VOB_PDL_SWITCH(attention_flex)
 // the head's features are asked for before the token's position and slot are known (padding rows are rows of
 // the projection like any other).
 //   q, k:  the first `rot` features of a head are rotated, feature i with i + rot / 2, by
-//          float(pos) * inv_freq[i]; then (unit_rms) the head is divided by sqrt(mean(x^2) + eps);
+//          float(pos) * inv_freq[i]; then (unit_rms) the head is divided by sqrt(mean(x^2) + eps) and, where a
+//          weight of D entries is given (`q_norm_w`, `k_norm_w`, shared by the heads), multiplied by it;
 //          q is also multiplied by 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) (temp_every > 0).
 //   v:     v_mode 1: the values are also left in `v_first` [T, G * DV] for later layers of this step;
 //          v_mode 2: v <- (1 - lambda) v + lambda v_first, lambda = *vmix.
-// Rows with a negative position (padding) are left alone; a negative slot skips the cache write.
+// Rows with a negative position (padding) are left alone; a negative slot skips the cache write. Without a cache
+// (a layer that reads the keys and values another layer wrote) only the queries are prepared.
 // ---------------------------------------------------------------------------------------------
 // NI: features a lane holds of a q or k head, 32 * NI >= D.
 template <typename T, int NI>
 __global__ void __launch_bounds__(256, 4)
 flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int v_off, const int* __restrict__ positions,
                  const int* __restrict__ slots, const float* __restrict__ inv_freq, int rot, int unit_rms, float eps,
-                 float temp_coef, int temp_every, const float* __restrict__ vmix, T* __restrict__ v_first, int v_mode,
-                 T* __restrict__ q_out, long ld_q, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D, int DV,
+                 float temp_coef, int temp_every, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+                 const float* __restrict__ vmix, T* __restrict__ v_first, int v_mode, T* __restrict__ q_out, long ld_q, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D, int DV,
                  int page_size) {
     pdl_launch_dependents();
     pdl_wait(61);
@@ -45,7 +50,7 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
     const int half = rot >> 1;
     {
         const int job = blockIdx.y * 8 + warp;
-        if (job >= H + 2 * G) return;
+        if (job >= (kcache ? H + 2 * G : H)) return;       // no cache given: only the queries are prepared
         if (job < H + G) {
             const bool is_q = job < H;
             const int head = is_q ? job : job - H;
@@ -73,6 +78,7 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
             float mul = 1.f;
             if (unit_rms) mul = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
             if (is_q && temp_every > 0) mul *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+            const float* nw = is_q ? q_norm_w : k_norm_w;
             T* dst;
             if (is_q) {
                 dst = q_out + (size_t)t * ld_q + (size_t)head * D;
@@ -83,7 +89,7 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
                 const int f = lane + 32 * i;
-                if (f < D) st_f(dst + f, x[i] * mul);
+                if (f < D) st_f(dst + f, nw ? x[i] * mul * nw[f] : x[i] * mul);
             }
         } else {
             if (pos < 0) return;
@@ -104,7 +110,8 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
 
 VOB_EXPORT int vob_flex_prep(const void* proj, int code, long ld, int q_off, int k_off, int v_off, const int* positions,
                              const int* slots, const float* inv_freq, int rot, int unit_rms, float eps, float temp_coef,
-                             int temp_every, const float* vmix, void* v_first, int v_mode, void* q_out, long ld_q, void* kcache,
+                             int temp_every, const float* q_norm_w, const float* k_norm_w, const float* vmix, void* v_first,
+                             int v_mode, void* q_out, long ld_q, void* kcache,
                              void* vcache, int T, int H, int G, int D, int DV, int page_size, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || D <= 0 || DV <= 0 || page_size <= 0 || rot < 0 || rot > D || (rot & 1)) return VOB_ERR_BAD_ARG;
@@ -116,7 +123,8 @@ VOB_EXPORT int vob_flex_prep(const void* proj, int code, long ld, int q_off, int
 #define VOB_PREP(NI_)                                                                                                                  \
     VOB_DISPATCH_ELEM(code, return vob_launch(flex_prep_kernel<ElemT, NI_>, dim3(T, (H + 2 * G + 7) / 8), dim3(256), 0, stream,              \
                                               (const ElemT*)proj, ld, q_off, k_off, v_off, positions, slots, inv_freq, rot, unit_rms, eps,  \
-                                              temp_coef, temp_every, vmix, (ElemT*)v_first, v_mode, (ElemT*)q_out, ld_q, (ElemT*)kcache,   \
+                                              temp_coef, temp_every, q_norm_w, k_norm_w, vmix, (ElemT*)v_first, v_mode, (ElemT*)q_out,  \
+                                              ld_q, (ElemT*)kcache,                                                                      \
                                               (ElemT*)vcache, H, G, D, DV, page_size))
     if (D <= 32) VOB_PREP(1);
     else if (D <= 64) VOB_PREP(2);
@@ -164,7 +172,8 @@ flex_attention_warp_kernel(const T* __restrict__ q, long q_stride, T* __restrict
                            const T* __restrict__ kcache, const T* __restrict__ vcache, const int* __restrict__ block_tables,
                            int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions, int T_rows, int H,
                            int G, int D, int DV, int page_size, int window, float scale, const float* __restrict__ sink,
-                           const T* __restrict__ gate, long gate_stride, float out_scale) {
+                           const T* __restrict__ gate, long gate_stride, float out_scale, int chunk, float softcap,
+                           const float* __restrict__ dist_r1, const float* __restrict__ dist_r2) {
     pdl_launch_dependents();
     pdl_wait(62);
     extern __shared__ float qs_all[];
@@ -185,7 +194,9 @@ flex_attention_warp_kernel(const T* __restrict__ q, long q_stride, T* __restrict
     __syncwarp();
     const int seq = row_seq[row];
     const int* bt = block_tables + (size_t)seq * max_pages;
-    const int first = window > 0 ? max(0, pos + 1 - window) : 0;
+    int first = window > 0 ? max(0, pos + 1 - window) : 0;
+    if (chunk > 0) first = max(first, pos - pos % chunk);
+    const float r1 = dist_r1 ? dist_r1[head] : 0.f, r2 = dist_r1 ? dist_r2[head] : 0.f;
 
     constexpr int VN = Vec16<T>::N;
     const bool vec = D % VN == 0;                    // a key row then starts on a 16-byte boundary
@@ -215,6 +226,8 @@ flex_attention_warp_kernel(const T* __restrict__ q, long q_stride, T* __restrict
                 for (int d = 0; d < D; ++d) dot = fmaf(qs[d], ld_f(kp + d), dot);
             }
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            if (dist_r1) s -= r1 * log1pf(r2 * (float)(pos - j));
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -259,10 +272,12 @@ flex_attention_warp_kernel(const T* __restrict__ q, long q_stride, T* __restrict
 VOB_EXPORT int vob_flex_attention(const void* q, long q_stride, void* out, long out_stride, const void* kcache, const void* vcache,
                                   int code, const int* block_tables, int max_pages, const int* row_seq, const int* positions,
                                   int T_rows, int H, int G, int D, int DV, int page_size, int window, float scale,
-                                  const float* sink, const void* gate, long gate_stride, float out_scale, cudaStream_t stream) {
+                                  const float* sink, const void* gate, long gate_stride, float out_scale, int chunk, float softcap,
+                                  const float* dist_r1, const float* dist_r2, cudaStream_t stream) {
     if (T_rows <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || max_pages <= 0 || D <= 0 || DV <= 0) return VOB_ERR_BAD_ARG;
     if (D > 256 || DV > 256) return VOB_ERR_UNSUPPORTED;
+    if (chunk < 0 || softcap < 0.f || (dist_r1 != nullptr) != (dist_r2 != nullptr)) return VOB_ERR_BAD_ARG;
     const long long warps = (long long)T_rows * H;
     const long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) return VOB_ERR_UNSUPPORTED;
@@ -270,6 +285,7 @@ VOB_EXPORT int vob_flex_attention(const void* q, long q_stride, void* out, long 
     VOB_DISPATCH_ELEM(code, return vob_launch(flex_attention_warp_kernel<ElemT>, dim3((unsigned)blocks), dim3(128), smem, stream,
                                               (const ElemT*)q, q_stride, (ElemT*)out, out_stride, (const ElemT*)kcache,
                                               (const ElemT*)vcache, block_tables, max_pages, row_seq, positions, T_rows, H, G, D, DV,
-                                              page_size, window, scale, sink, (const ElemT*)gate, gate_stride, out_scale));
+                                              page_size, window, scale, sink, (const ElemT*)gate, gate_stride, out_scale, chunk, softcap,
+                                              dist_r1, dist_r2));
     return 0;
 }

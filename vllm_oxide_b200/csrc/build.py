@@ -32,7 +32,7 @@ if os.environ.get("VOB_TIMELINE") == "1":      # per-kernel timeline recording (
 _CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
 
 CUDA_MODULES = ("elementwise", "gemm_f32", "attention", "attention_mma", "attention_sm100", "sampling", "gemm_sm100", "gemm_sm100_pair",
-                "streams", "recurrence", "latent_attention", "attention_flex")
+                "streams", "recurrence", "latent_attention", "attention_flex", "moe")
 _lock = threading.Lock()
 _loaded: Dict[str, object] = {}
 

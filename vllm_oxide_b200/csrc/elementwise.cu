@@ -9,30 +9,43 @@
 VOB_PDL_SWITCH(elementwise)
 
 // ---------------------------------------------------------------------------------------------
-// Embedding gather: out[t, :] = table[tokens[t], :] * scale   (float32 out; scale 1 leaves the row as it is)
+// Embedding gather: out[t, :] = table[tokens[t], :] * scale (+ pos_table[positions[t], :])   (float32 out; scale 1 leaves
+// the row as it is). The learned position vector is optional; a row with a negative position (padding) gets none.
 // Reference op: crates/engine/src/backend/cpu/mod.rs:172-180.
 // Launch: one block per token, 256 threads. Bound: memory (2 * h * 4 bytes per token).
-// A token outside [0, vocab) writes zeros and raises *err_flag (the host checks ids first).
+// A token outside [0, vocab) writes zeros and raises *err_flag (the host checks ids first); so does a position
+// beyond the table.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int h, int vocab, int* err_flag, float scale) {
+                             float* __restrict__ out, int h, int vocab, int* err_flag, float scale,
+                             const T* __restrict__ pos_table, const int* __restrict__ positions, int max_pos) {
     pdl_launch_dependents();
     pdl_wait(1);
     int t = blockIdx.x;
     int tok = tokens[t];
-    bool ok = tok >= 0 && tok < vocab;
+    int pos = pos_table ? positions[t] : -1;
+    bool ok = tok >= 0 && tok < vocab && pos < max_pos;
     if (!ok && threadIdx.x == 0 && err_flag) atomicExch(err_flag, 1);
     const T* src = table + (size_t)(ok ? tok : 0) * h;
+    const T* psrc = (ok && pos >= 0) ? pos_table + (size_t)pos * h : nullptr;
     float* dst = out + (size_t)t * h;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = ok ? ld_f(src + i) * scale : 0.f;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+        float v = ok ? ld_f(src + i) * scale : 0.f;
+        if (psrc) v += ld_f(psrc + i);
+        dst[i] = v;
+    }
 }
 
 VOB_EXPORT int vob_embed(const void* table, int table_code, const int* tokens, float* out, int T, int h,
-                         int vocab, int* err_flag, float scale, cudaStream_t stream) {
+                         int vocab, int* err_flag, float scale, const void* pos_table, const int* positions, int max_pos,
+                         cudaStream_t stream) {
     if (T <= 0) return 0;
     if (h <= 0 || vocab <= 0) return VOB_ERR_BAD_ARG;
-    VOB_DISPATCH_ELEM(table_code, return vob_launch(embed_kernel<ElemT>, dim3(T), dim3(256), 0, stream, (const ElemT*)table, tokens, out, h, vocab, err_flag, scale));
+    if (pos_table && (!positions || max_pos <= 0)) return VOB_ERR_BAD_ARG;
+    if (!pos_table) max_pos = 0x7fffffff;
+    VOB_DISPATCH_ELEM(table_code, return vob_launch(embed_kernel<ElemT>, dim3(T), dim3(256), 0, stream, (const ElemT*)table, tokens, out, h, vocab, err_flag, scale,
+                                                    (const ElemT*)pos_table, positions, max_pos));
     return 0;
 }
 
@@ -591,4 +604,127 @@ VOB_EXPORT int vob_glu(const void* in, long long in_stride, void* out, int code,
     if (code == VOB_F32) return launch_swiglu<float, 1>(in, in_stride, out, T, I, stream);
     if (code == VOB_BF16) return launch_swiglu<__nv_bfloat16, 1>(in, in_stride, out, T, I, stream);
     return VOB_ERR_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layer norm with weight and bias, LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * w + b, in two arrangements:
+//   delta given:  y = LN(delta[r]);  resid[r] += y  (the residual takes the NORMED result of a sub-layer, float32);
+//                 copy[r] = resid[r] in the activations' type, if `copy` is given (what the next sub-layer reads)
+//   delta null:   out[r] = LN(resid[rows ? rows[r] : r])   (the model's last norm on the wanted rows)
+// Launch: one block of 256 threads per row, h floats of shared memory; the mean first, then the mean of the squared
+// deviations from it, each a strided partial sum per thread and a fixed tree, so a row's value is the same in every batch.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    __syncthreads();                       // red may still be read from the call before
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i];
+    return t;
+}
+
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
+                 const float* __restrict__ bias, const int* __restrict__ rows, TO* __restrict__ out, int h, float eps) {
+    pdl_launch_dependents();
+    pdl_wait(5);
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* x = resid + (size_t)src * h;
+    const TD* d = delta ? delta + (size_t)r * h : nullptr;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+        const float v = d ? ld_f(d + i) : x[i];
+        row[i] = v;
+        s += v;
+    }
+    const float mean = block_sum_256(s, red) / (float)h;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+        const float c = row[i] - mean;
+        ss = fmaf(c, c, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum_256(ss, red) / (float)h + eps);
+    TO* o = out ? out + (size_t)r * h : nullptr;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) {
+        float y = (row[i] - mean) * inv * weight[i] + bias[i];
+        if (d) {
+            y += x[i];
+            x[i] = y;
+        }
+        if (o) st_f(o + i, y);
+    }
+}
+
+VOB_EXPORT int vob_layernorm(float* resid, const void* delta, int delta_code, const float* weight, const float* bias,
+                             const int* rows, void* out, int out_code, int R, int h, float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (h <= 0 || !weight || !bias || (delta && rows) || (!delta && !out)) return VOB_ERR_BAD_ARG;
+    const size_t smem = (size_t)h * sizeof(float);
+    if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
+    if (!delta) delta_code = VOB_F32;
+    if (!out) out_code = VOB_F32;
+#define VOB_LN(TD_, TO_) return vob_launch(layernorm_kernel<TD_, TO_>, dim3(R), dim3(256), smem, stream, resid, (const TD_*)delta, weight, bias, rows, (TO_*)out, h, eps)
+    if (delta_code == VOB_F32 && out_code == VOB_F32) VOB_LN(float, float);
+    if (delta_code == VOB_BF16 && out_code == VOB_BF16) VOB_LN(__nv_bfloat16, __nv_bfloat16);
+    if (delta_code == VOB_F32 && out_code == VOB_BF16) VOB_LN(float, __nv_bfloat16);
+    if (delta_code == VOB_BF16 && out_code == VOB_F32) VOB_LN(__nv_bfloat16, float);
+#undef VOB_LN
+    return VOB_ERR_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The float32 residual in the activations' type: out[i] = in[i] (rounded to nearest even for bfloat16). What a
+// sub-layer that reads the residual itself is given where nothing before it has left such a copy.
+// ---------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256) cast_rows_kernel(const float* __restrict__ in, TO* __restrict__ out, long long n) {
+    pdl_launch_dependents();
+    pdl_wait(6);
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) st_f(out + i, in[i]);
+}
+
+VOB_EXPORT int vob_cast_rows(const float* in, void* out, int out_code, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL) return VOB_ERR_UNSUPPORTED;
+    VOB_DISPATCH_ELEM(out_code, return vob_launch(cast_rows_kernel<ElemT>, dim3((unsigned)blocks), dim3(256), 0, stream, in, (ElemT*)out, n));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Activations of a feed-forward that is not gated, element by element, float32 arithmetic:
+//   act 0, xIELU with two numbers ap = params[0] > 0 and an = params[1]:
+//       z > 0:  ap z^2 + z / 2;      z <= 0:  an (exp(z) - 1 - z) + z / 2
+// in [T, I] with a row stride, out [T, I] contiguous (may be `in` itself when that is contiguous).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I, int act, const float* __restrict__ params) {
+    pdl_launch_dependents();
+    pdl_wait(7);
+    const int t = blockIdx.x;
+    const int j = blockIdx.y * 256 + threadIdx.x;
+    if (j >= I) return;
+    const float ap = params[0], an = params[1];
+    const float z = ld_f(in + (size_t)t * in_stride + j);
+    const float y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    st_f(out + (size_t)t * I + j, y);
+}
+
+VOB_EXPORT int vob_act(const void* in, long long in_stride, void* out, int code, int T, int I, int act, const float* params,
+                       cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (I <= 0 || act != 0 || !params) return VOB_ERR_BAD_ARG;
+    if ((I + 255) / 256 > 65535) return VOB_ERR_UNSUPPORTED;
+    VOB_DISPATCH_ELEM(code, return vob_launch(act_kernel<ElemT>, dim3(T, (I + 255) / 256), dim3(256), 0, stream, (const ElemT*)in, in_stride,
+                                              (ElemT*)out, I, act, params));
+    return 0;
 }

@@ -124,6 +124,8 @@ VOB_EXPORT int vob_delta_prep(const void* proj, int code, long ld, int k_off, in
 //   v = silu(y_v) (in the activations' type)
 //   strength[h] = sigmoid(proj[b_off + h])
 //   decay[h, c] = exp(-exp(a_log[h]) * softplus(low[a_off + h K + c] + dt_bias[h K + c]))
+//   or, with one decay per head (`decay_per_head`): decay[h, c] = exp(-exp(a_log[h]) * softplus(low[a_off + h] + dt_bias[h]))
+//   for every c (the scan reads a decay per key channel either way)
 // `low` [T, ld_low] is the output of the second, low-rank projections. Rows with a negative position
 // (padding) are skipped. Launch: grid (tokens, ceil(jobs / 4)), blocks of 128 threads; a warp takes one
 // head (or one head's decays, or the strengths) of one token. K up to 512.
@@ -136,7 +138,7 @@ gated_delta_prep_kernel(const T* __restrict__ proj, long ld, int x_off, int b_of
                         const float* __restrict__ dt_bias, const int* __restrict__ positions, const int* __restrict__ row_seq,
                         const int* __restrict__ seq_starts, const int* __restrict__ state_slots, int H, int G, int K, int V,
                         float* __restrict__ q_out, float* __restrict__ k_out, T* __restrict__ v_out, float* __restrict__ decay,
-                        float* __restrict__ strength) {
+                        float* __restrict__ strength, int decay_per_head) {
     pdl_launch_dependents();
     pdl_wait(45);
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -185,11 +187,18 @@ gated_delta_prep_kernel(const T* __restrict__ proj, long ld, int x_off, int b_of
         } else if (job < 2 * G + 2 * H) {            // a head's decays
             const int head = job - 2 * G - H;
             const float rate = expf(a_log[head]);
-            for (int f = lane; f < K; f += 32) {
-                const int ch = head * K + f;
-                const float z = ld_f(low + (size_t)t * ld_low + a_off + ch) + dt_bias[ch];
+            if (decay_per_head) {
+                const float z = ld_f(low + (size_t)t * ld_low + a_off + head) + dt_bias[head];
                 const float sp = z > 20.f ? z : log1pf(expf(z));
-                decay[(size_t)t * H * K + ch] = expf(-rate * sp);
+                const float d = expf(-rate * sp);
+                for (int f = lane; f < K; f += 32) decay[(size_t)t * H * K + head * K + f] = d;
+            } else {
+                for (int f = lane; f < K; f += 32) {
+                    const int ch = head * K + f;
+                    const float z = ld_f(low + (size_t)t * ld_low + a_off + ch) + dt_bias[ch];
+                    const float sp = z > 20.f ? z : log1pf(expf(z));
+                    decay[(size_t)t * H * K + ch] = expf(-rate * sp);
+                }
             }
         } else {                                     // writing strengths
             for (int h = lane; h < H; h += 32)
@@ -202,7 +211,7 @@ VOB_EXPORT int vob_gated_delta_prep(const void* proj, int code, long ld, int x_o
                                     const float* cw, int taps, const float* cstate, const float* a_log, const float* dt_bias,
                                     const int* positions, const int* row_seq, const int* seq_starts, const int* state_slots, int T,
                                     int H, int G, int K, int V, float* q_out, float* k_out, void* v_out, float* decay,
-                                    float* strength, cudaStream_t stream) {
+                                    float* strength, int decay_per_head, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || K <= 0 || V <= 0 || taps < 1 || H % G != 0) return VOB_ERR_BAD_ARG;
     if (K > 512) return VOB_ERR_UNSUPPORTED;
@@ -211,7 +220,7 @@ VOB_EXPORT int vob_gated_delta_prep(const void* proj, int code, long ld, int x_o
     VOB_DISPATCH_ELEM(code, return vob_launch(gated_delta_prep_kernel<ElemT, NI_>, dim3(T, (2 * G + 2 * H + 1 + 3) / 4), dim3(128), 0,       \
                                               stream, (const ElemT*)proj, ld, x_off, b_off, (const ElemT*)low, ld_low, a_off, cw, taps,     \
                                               cstate, a_log, dt_bias, positions, row_seq, seq_starts, state_slots, H, G, K, V, q_out, k_out, \
-                                              (ElemT*)v_out, decay, strength))
+                                              (ElemT*)v_out, decay, strength, decay_per_head))
     if (K <= 32) VOB_GDPREP(1);
     else if (K <= 64) VOB_GDPREP(2);
     else if (K <= 128) VOB_GDPREP(4);

@@ -31,6 +31,7 @@ PYBIND11_MODULE(VOB_MODULE_NAME, m) {
         .def_readwrite("num_pages", &GroupSpec::num_pages);
     m.attr("FULL") = (int)kFull;
     m.attr("WINDOW") = (int)kWindow;
+    m.attr("CHUNK") = (int)kChunk;
 
     py::class_<CacheManager>(m, "CacheManager")
         .def(py::init<int, std::vector<GroupSpec>, int>(), py::arg("page_size"), py::arg("groups"), py::arg("num_state_slots"))

@@ -12,7 +12,10 @@
 // and every request has one block table per group:
 //   Full   - every key is kept while the request lives;
 //   Window - only the last `window` keys are read, so a page is given back as soon as every
-//            position in it has fallen out of the window of the next query.
+//            position in it has fallen out of the window of the next query;
+//   Chunk  - positions are cut into blocks of `window` counted from 0 and a query reads the keys
+//            of its own block only, so a page is given back once the next query's block starts
+//            behind it.
 // Beside the pages, each admitted request holds one state slot (an index below
 // `num_state_slots`) for per-request state of fixed size.
 #pragma once
@@ -26,7 +29,7 @@
 
 namespace vob {
 
-enum GroupKind : int { kFull = 0, kWindow = 1 };
+enum GroupKind : int { kFull = 0, kWindow = 1, kChunk = 2 };
 
 // What a group keeps of a request. The two questions every other piece of the runtime asks of a
 // kind are answered HERE and nowhere else (the cache manager's `commit`, the scheduler's capacity
@@ -34,18 +37,20 @@ enum GroupKind : int { kFull = 0, kWindow = 1 };
 // functions.
 struct GroupSpec {
     int kind = kFull;
-    int window = 0;      // keys visible to a query, itself included (Window groups)
+    int window = 0;      // keys visible to a query, itself included (Window groups); the block length (Chunk groups)
     int num_pages = 0;
 
     // First position whose key a query at position `pos` still reads.
     int64_t first_visible(int64_t pos) const {
         if (kind == kWindow) return std::max<int64_t>(0, pos + 1 - window);
+        if (kind == kChunk) return pos - pos % window;
         return 0;
     }
     // Most tokens whose pages a request of `total` tokens holds at any one time: a window group
-    // holds the window plus the page being filled, a full group everything.
+    // holds the window plus the page being filled, a chunk group one block plus the page it
+    // starts in the middle of, a full group everything.
     int64_t max_live_tokens(int64_t total, int page_size) const {
-        if (kind == kWindow) return std::min<int64_t>(total, (int64_t)window + page_size);
+        if (kind == kWindow || kind == kChunk) return std::min<int64_t>(total, (int64_t)window + page_size);
         return total;
     }
 };
@@ -101,7 +106,8 @@ public:
         for (const auto& g : groups_) {
             if (g.num_pages <= 0) throw CacheError("a cache group needs at least one page");
             if (g.kind == kWindow && g.window <= 0) throw CacheError("a window group needs a positive window");
-            if (g.kind != kFull && g.kind != kWindow) throw CacheError("unknown cache group kind");
+            if (g.kind == kChunk && g.window <= 0) throw CacheError("a chunk group needs a positive block length");
+            if (g.kind != kFull && g.kind != kWindow && g.kind != kChunk) throw CacheError("unknown cache group kind");
             pools_.emplace_back(g.num_pages);
         }
         for (int s = num_state_slots - 1; s >= 0; --s) free_slots_.push_back(s);

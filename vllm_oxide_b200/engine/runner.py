@@ -106,6 +106,9 @@ class ModelRunner:
         # max_position_embeddings (crates/engine/src/backend/cpu/mod.rs:49-54): rotation angles are
         # computed from the position itself, so no table length binds them.
         self.max_model_len = engine.max_model_len
+        table = getattr(self.spec.embedding, "pos_table", None)
+        if table is not None:                    # a table of learned positions does bind the length
+            self.max_model_len = min(self.max_model_len, int(table.shape[0]))
         self.pools = CachePools(self.spec, engine.block_size, engine.max_seqs, self.dtype, self.device,
                                 num_pages=engine.num_pages, pool_bytes=engine.kv_pool_bytes)
         self.manager = self.pools.manager

@@ -91,7 +91,7 @@ def _int32_vec(t: torch.Tensor, n: int, op: str, name: str) -> None:
 
 _fn_cache = {}
 _MODULES = ("elementwise", "gemm_f32", "gemm_sm100", "gemm_sm100_pair", "attention", "attention_mma", "attention_sm100", "sampling",
-            "streams", "recurrence", "latent_attention", "attention_flex")
+            "streams", "recurrence", "latent_attention", "attention_flex", "moe")
 
 # Per-op device timing, off unless a profile is being taken: CUDA events around each wrapper
 # (the reference times ops by wall clock on the CPU and notes that a CUDA backend must use
@@ -202,19 +202,27 @@ def set_pdl(on: bool) -> None:
 # ------------------------------------------------------------------------------------ embedding
 @_timed
 def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, err_flag: Optional[torch.Tensor] = None,
-          scale: float = 1.0) -> None:
-    """out[t] = table[tokens[t]] * scale as float32; `tokens` int32 [T], `out` float32 [T, h]."""
+          scale: float = 1.0, pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[tokens[t]] * scale (+ pos_table[positions[t]]) as float32; `tokens` int32 [T], `out` float32 [T, h].
+    `pos_table` [max positions, h] of the table's type: a learned vector per position (rows of negative position get none)."""
     op = "embed"
-    _cuda(op, table, tokens, out, err_flag)
+    _cuda(op, table, tokens, out, err_flag, pos_table, positions)
+    if pos_table is not None:
+        if pos_table.dim() != 2 or pos_table.shape[1] != table.shape[1] or pos_table.dtype != table.dtype or not pos_table.is_contiguous():
+            raise ShapeError(op, f"pos_table must be contiguous {table.dtype} [positions, {table.shape[1]}], got {pos_table.dtype} {list(pos_table.shape)}")
+        if positions is None:
+            raise ShapeError(op, "a position table needs the rows' positions")
+        _int32_vec(positions, out.shape[0], op, "positions")
     T = out.shape[0]
     if table.dim() != 2 or not table.is_contiguous():
         raise ShapeError(op, f"table must be contiguous [vocab, h], got {list(table.shape)}")
     _int32_vec(tokens, T, op, "tokens")
     if out.dtype != torch.float32 or out.dim() != 2 or out.shape[1] != table.shape[1] or not out.is_contiguous():
         raise ShapeError(op, f"out must be contiguous float32 [T, {table.shape[1]}], got {out.dtype} {list(out.shape)}")
-    f = _fn("elementwise", "vob_embed", [_P, _I, _P, _P, _I, _I, _I, _P, _F, _P])
+    f = _fn("elementwise", "vob_embed", [_P, _I, _P, _P, _I, _I, _I, _P, _F, _P, _P, _I, _P])
     _check(f(_ptr(table), _code(table, op), _ptr(tokens), _ptr(out), T, table.shape[1], table.shape[0],
-             _ptr(err_flag), float(scale), _stream()), op)
+             _ptr(err_flag), float(scale), _ptr(pos_table), _ptr(positions) if pos_table is not None else _P(0),
+             pos_table.shape[0] if pos_table is not None else 0, _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ norm
@@ -246,6 +254,83 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
     f = _fn("elementwise", "vob_add_rmsnorm", [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, _P])
     _check(f(_ptr(resid), _ptr(delta), _code(delta, op) if delta is not None else 0, _ptr(weight), _ptr(rows),
              _ptr(out), _code(out, op), R, h, float(eps), _ptr(delta_scale), _stream()), op)
+
+
+@_timed
+def layernorm_add(resid: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                  copy: Optional[torch.Tensor] = None) -> None:
+    """resid += LN(delta) with LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * weight + bias; `copy` ([T, h] in the
+    activations' type), if given, receives the new residual."""
+    op = "layernorm_add"
+    _cuda(op, resid, delta, weight, bias, copy)
+    if resid.dtype != torch.float32 or resid.dim() != 2 or not resid.is_contiguous():
+        raise ShapeError(op, f"the residual must be contiguous float32 [T, h], got {resid.dtype} {list(resid.shape)}")
+    T, h = resid.shape
+    _f32_vec(weight, h, op, "weight")
+    _f32_vec(bias, h, op, "bias")
+    if delta.shape != resid.shape or not delta.is_contiguous():
+        raise ShapeError(op, f"delta must be contiguous {list(resid.shape)}, got {list(delta.shape)}")
+    if copy is not None and (copy.shape != resid.shape or not copy.is_contiguous()):
+        raise ShapeError(op, f"copy must be contiguous {list(resid.shape)}, got {list(copy.shape)}")
+    if h * 4 > 48 * 1024:
+        raise ShapeError(op, f"width {h} is beyond this kernel's limit of {48 * 1024 // 4}")
+    f = _fn("elementwise", "vob_layernorm", [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _F, _P])
+    _check(f(_ptr(resid), _ptr(delta), _code(delta, op), _ptr(weight), _ptr(bias), _P(0), _ptr(copy),
+             _code(copy, op) if copy is not None else 0, T, h, float(eps), _stream()), op)
+
+
+@_timed
+def layernorm_rows(resid: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+                   rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = LN(resid[rows[r]]) (every row in order without `rows`); the residual is left as it is."""
+    op = "layernorm_rows"
+    _cuda(op, resid, weight, bias, out, rows)
+    if resid.dtype != torch.float32 or resid.dim() != 2 or not resid.is_contiguous():
+        raise ShapeError(op, f"the residual must be contiguous float32 [T, h], got {resid.dtype} {list(resid.shape)}")
+    T, h = resid.shape
+    _f32_vec(weight, h, op, "weight")
+    _f32_vec(bias, h, op, "bias")
+    R = T
+    if rows is not None:
+        R = rows.numel()
+        _int32_vec(rows, R, op, "rows")
+    if out.dim() != 2 or out.shape[0] < R or out.shape[1] != h or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous [>={R}, {h}], got {list(out.shape)}")
+    if h * 4 > 48 * 1024:
+        raise ShapeError(op, f"width {h} is beyond this kernel's limit of {48 * 1024 // 4}")
+    f = _fn("elementwise", "vob_layernorm", [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _F, _P])
+    _check(f(_ptr(resid), _P(0), 0, _ptr(weight), _ptr(bias), _ptr(rows), _ptr(out), _code(out, op), R, h, float(eps), _stream()), op)
+
+
+@_timed
+def cast_rows(src: torch.Tensor, out: torch.Tensor) -> None:
+    """out = src (float32, contiguous) in out's type, element by element."""
+    op = "cast_rows"
+    _cuda(op, src, out)
+    if src.dtype != torch.float32 or not src.is_contiguous() or out.shape != src.shape or not out.is_contiguous():
+        raise ShapeError(op, f"a contiguous float32 source and a contiguous result of its shape are needed, got {src.dtype} "
+                             f"{list(src.shape)} and {list(out.shape)}")
+    f = _fn("elementwise", "vob_cast_rows", [_P, _P, _I, _L, _P])
+    _check(f(_ptr(src), _ptr(out), _code(out, op), src.numel(), _stream()), op)
+
+
+ACTIVATIONS = {"xielu": 0}
+
+
+@_timed
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str, params: torch.Tensor) -> None:
+    """out[t, j] = act(x[t, j]), float32 arithmetic. "xielu" with params = float32 [ap, an] on the device:
+    z > 0: ap z^2 + z / 2; z <= 0: an (exp(z) - 1 - z) + z / 2. `out` may be `x` itself."""
+    op = "activation"
+    _cuda(op, x, out, params)
+    _rows_2d(x, op, "x")
+    if kind not in ACTIVATIONS:
+        raise ShapeError(op, f"activation {kind!r} is not known ({', '.join(ACTIVATIONS)})")
+    if out.shape != x.shape or out.dtype != x.dtype or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous {x.dtype} {list(x.shape)}, got {out.dtype} {list(out.shape)}")
+    _f32_vec(params, 2, op, "params")
+    f = _fn("elementwise", "vob_act", [_P, _L, _P, _I, _I, _I, _I, _P, _P])
+    _check(f(_ptr(x), x.stride(0), _ptr(out), _code(out, op), x.shape[0], x.shape[1], ACTIVATIONS[kind], _ptr(params), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ rope + cache write
@@ -914,14 +999,15 @@ def gated_delta_prep(proj: torch.Tensor, x_off: int, b_off: int, low: torch.Tens
                      conv_state: Optional[torch.Tensor], a_log: torch.Tensor, dt_bias: torch.Tensor, positions: torch.Tensor,
                      row_seq: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, heads: int,
                      rk_heads: int, dim: int, vdim: int, q_out: torch.Tensor, k_out: torch.Tensor, v_out: torch.Tensor,
-                     decay: torch.Tensor, strength: torch.Tensor) -> None:
+                     decay: torch.Tensor, strength: torch.Tensor, decay_per_head: bool = False) -> None:
     """What the gated delta rule reads, per token. Columns x_off.. of `proj` [T, ld] hold q, k (rk_heads heads of
     `dim` each) and v (heads of `vdim`) side by side: each channel passes a causal convolution over the request's
     tokens (conv_w float32 [C, taps], last column the current token's; inputs before the step's first row from
     conv_state float32 [slots, taps - 1, C]) and silu; q and k are then scaled to unit length per head (1e-6 under
     the root), q also by dim^-1/2. strength = sigmoid(proj[b_off + h]); decay = exp(-exp(a_log[h]) *
     softplus(low[a_off + h * dim + c] + dt_bias)). q_out, k_out float32 [T, rk_heads * dim]; v_out [T, heads * vdim]
-    in proj's type; decay float32 [T, heads * dim]; strength float32 [T, heads]."""
+    in proj's type; decay float32 [T, heads * dim]; strength float32 [T, heads]. `decay_per_head`: one decay per head,
+    exp(-exp(a_log[h]) * softplus(low[a_off + h] + dt_bias[h])), written to all of the head's key channels."""
     op = "gated_delta_prep"
     _cuda(op, proj, low, conv_w, conv_state, a_log, dt_bias, positions, row_seq, seq_starts, state_slots, q_out, k_out, v_out, decay, strength)
     _rows_2d(proj, op, "proj")
@@ -934,12 +1020,13 @@ def gated_delta_prep(proj: torch.Tensor, x_off: int, b_off: int, low: torch.Tens
     if taps > 1 and (conv_state is None or conv_state.dtype != torch.float32 or conv_state.dim() != 3 or conv_state.shape[1:] != (taps - 1, C)
                      or not conv_state.is_contiguous()):
         raise ShapeError(op, f"conv_state must be contiguous float32 [slots, {taps - 1}, {C}]")
-    if low.dtype != proj.dtype or low.shape[0] != T or a_off < 0 or a_off + heads * dim > low.shape[1]:
-        raise ShapeError(op, f"low must be {proj.dtype} [{T}, >= {a_off + heads * dim}], got {low.dtype} {list(low.shape)}")
+    n_decay = heads if decay_per_head else heads * dim
+    if low.dtype != proj.dtype or low.shape[0] != T or a_off < 0 or a_off + n_decay > low.shape[1]:
+        raise ShapeError(op, f"low must be {proj.dtype} [{T}, >= {a_off + n_decay}], got {low.dtype} {list(low.shape)}")
     if x_off < 0 or x_off + C > proj.shape[1] or b_off < 0 or b_off + heads > proj.shape[1]:
         raise ShapeError(op, f"columns {x_off}..{x_off + C} or {b_off}..{b_off + heads} lie outside proj's {proj.shape[1]}")
     _f32_vec(a_log, heads, op, "a_log")
-    _f32_vec(dt_bias, heads * dim, op, "dt_bias")
+    _f32_vec(dt_bias, n_decay, op, "dt_bias")
     for name, t, cols in (("q_out", q_out, rk_heads * dim), ("k_out", k_out, rk_heads * dim), ("decay", decay, heads * dim),
                           ("strength", strength, heads)):
         if t.dtype != torch.float32 or t.shape != (T, cols) or not t.is_contiguous():
@@ -951,10 +1038,11 @@ def gated_delta_prep(proj: torch.Tensor, x_off: int, b_off: int, low: torch.Tens
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
     _int32_vec(state_slots, num_seqs, op, "state_slots")
     f = _fn("recurrence", "vob_gated_delta_prep", [_P, _I, _L, _I, _I, _P, _L, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
-                                                   _P, _P, _P, _P, _P, _P])
+                                                   _P, _P, _P, _P, _P, _I, _P])
     _check(f(_ptr(proj), _code(proj, op), proj.stride(0), x_off, b_off, _ptr(low), low.stride(0), a_off, _ptr(conv_w), taps,
              _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(positions), _ptr(row_seq), _ptr(seq_starts), _ptr(state_slots), T,
-             heads, rk_heads, dim, vdim, _ptr(q_out), _ptr(k_out), _ptr(v_out), _ptr(decay), _ptr(strength), _stream()), op)
+             heads, rk_heads, dim, vdim, _ptr(q_out), _ptr(k_out), _ptr(v_out), _ptr(decay), _ptr(strength),
+             1 if decay_per_head else 0, _stream()), op)
 
 
 @_timed
@@ -975,6 +1063,134 @@ def conv_state_update(proj: torch.Tensor, x_off: int, conv_state: torch.Tensor, 
     f = _fn("recurrence", "vob_conv_state_update", [_P, _I, _L, _I, _I, _I, _P, _P, _P, _I, _P])
     _check(f(_ptr(proj), _code(proj, op), proj.stride(0), x_off, C, conv_state.shape[1] + 1, _ptr(conv_state), _ptr(seq_starts),
              _ptr(state_slots), num_seqs, _stream()), op)
+
+
+# ------------------------------------------------------------------------------------ mixture of experts
+MOE_TILE_ROWS = 32           # rows of a tile of (token, expert) pairs (VOB_MOE_BM of csrc/moe.cu)
+
+
+def moe_sorted_rows(pairs: int, experts: int) -> int:
+    """Rows the ordered list of `pairs` (token, expert) pairs takes: every expert's run is padded to whole tiles."""
+    return -(-pairs // MOE_TILE_ROWS) * MOE_TILE_ROWS + experts * MOE_TILE_ROWS
+
+
+@_timed
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, positions: Optional[torch.Tensor], top: int, groups: int, keep: int,
+              renorm: bool, idx_out: torch.Tensor, w_out: torch.Tensor) -> None:
+    """Per row of x [T, width]: softmax over the E router logits (w_router float32 [E, width], float32 sums), election of
+    `top` experts among those of the `keep` best of `groups` runs of neighbours (groups <= 1: among all), weights = their
+    scores (renorm: divided by their sum). idx_out int32 [T, top] (-1 for rows of negative position), w_out float32 [T, top]."""
+    op = "moe_route"
+    _cuda(op, x, w_router, positions, idx_out, w_out)
+    _rows_2d(x, op, "x")
+    T, width = x.shape
+    if w_router.dtype != torch.float32 or w_router.dim() != 2 or w_router.shape[1] != width or not w_router.is_contiguous():
+        raise ShapeError(op, f"w_router must be contiguous float32 [experts, {width}], got {w_router.dtype} {list(w_router.shape)}")
+    E = w_router.shape[0]
+    if not 0 < top <= E:
+        raise ShapeError(op, f"{top} choices among {E} experts")
+    if groups > 1 and (E % groups or not 0 < keep <= groups or top > keep * (E // groups)):
+        raise ShapeError(op, f"{E} experts in {groups} groups of which {keep} are kept cannot give {top} choices")
+    if idx_out.dtype != torch.int32 or idx_out.shape != (T, top) or not idx_out.is_contiguous():
+        raise ShapeError(op, f"idx_out must be contiguous int32 [{T}, {top}], got {idx_out.dtype} {list(idx_out.shape)}")
+    if w_out.dtype != torch.float32 or w_out.shape != (T, top) or not w_out.is_contiguous():
+        raise ShapeError(op, f"w_out must be contiguous float32 [{T}, {top}], got {w_out.dtype} {list(w_out.shape)}")
+    if positions is not None:
+        _int32_vec(positions, T, op, "positions")
+    f = _fn("moe", "vob_moe_route", [_P, _I, _L, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P])
+    _check(f(_ptr(x), _code(x, op), x.stride(0), _ptr(w_router), _ptr(positions), T, width, E, int(top), int(groups), int(keep),
+             1 if renorm else 0, _ptr(idx_out), _ptr(w_out), _stream()), op)
+
+
+@_timed
+def moe_align(idx: torch.Tensor, experts: int, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, meta: torch.Tensor) -> None:
+    """The pairs idx [T, top] (expert of token t's k-th choice, -1: none) in order of their expert: sorted_pairs int32 [cap]
+    (pair number t * top + k, -1: padding; cap >= moe_sorted_rows(T * top, experts)), tile_expert int32 [cap / MOE_TILE_ROWS],
+    meta int32 [>= 1] (meta[0]: tiles in use)."""
+    op = "moe_align"
+    _cuda(op, idx, sorted_pairs, tile_expert, meta)
+    if idx.dtype != torch.int32 or idx.dim() != 2 or not idx.is_contiguous():
+        raise ShapeError(op, f"idx must be contiguous int32 [T, top], got {idx.dtype} {list(idx.shape)}")
+    P, cap = idx.numel(), sorted_pairs.numel()
+    if cap % MOE_TILE_ROWS or cap < moe_sorted_rows(P, experts):
+        raise ShapeError(op, f"sorted_pairs has {cap} rows, {moe_sorted_rows(P, experts)} (a multiple of {MOE_TILE_ROWS}) are needed")
+    _int32_vec(sorted_pairs, cap, op, "sorted_pairs")
+    _int32_vec(tile_expert, cap // MOE_TILE_ROWS, op, "tile_expert")
+    _int32_vec(meta, 1, op, "meta")
+    f = _fn("moe", "vob_moe_align", [_P, _I, _I, _P, _I, _P, _P, _P])
+    _check(f(_ptr(idx), P, int(experts), _ptr(sorted_pairs), cap, _ptr(tile_expert), _ptr(meta), _stream()), op)
+
+
+def _moe_tiles(op, sorted_pairs, tile_expert):
+    cap = sorted_pairs.numel()
+    _int32_vec(sorted_pairs, cap, op, "sorted_pairs")
+    if cap % MOE_TILE_ROWS:
+        raise ShapeError(op, f"sorted_pairs must hold whole tiles of {MOE_TILE_ROWS}, got {cap}")
+    _int32_vec(tile_expert, cap // MOE_TILE_ROWS, op, "tile_expert")
+    return cap // MOE_TILE_ROWS
+
+
+@_timed
+def moe_gate_up(x: torch.Tensor, w_gu: torch.Tensor, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, top: int,
+                h_out: torch.Tensor, tensor_cores: bool = False) -> None:
+    """h_out[pair] = silu(W_gate[e] x[token]) * (W_up[e] x[token]) for every pair of the ordered list; w_gu [E, 2 ff, width]
+    (an expert's gate rows, then its up rows) and h_out [T * top, ff] of x's type. `tensor_cores`: the bfloat16 tile form."""
+    op = "moe_gate_up"
+    _cuda(op, x, w_gu, sorted_pairs, tile_expert, h_out)
+    _rows_2d(x, op, "x")
+    T, width = x.shape
+    if w_gu.dim() != 3 or w_gu.shape[2] != width or w_gu.shape[1] % 2 or w_gu.dtype != x.dtype or not w_gu.is_contiguous():
+        raise ShapeError(op, f"w_gu must be contiguous {x.dtype} [experts, 2 ff, {width}], got {w_gu.dtype} {list(w_gu.shape)}")
+    ff = w_gu.shape[1] // 2
+    if h_out.shape != (T * top, ff) or h_out.dtype != x.dtype or not h_out.is_contiguous():
+        raise ShapeError(op, f"h_out must be contiguous {x.dtype} [{T * top}, {ff}], got {h_out.dtype} {list(h_out.shape)}")
+    if tensor_cores and x.dtype != torch.bfloat16:
+        raise ShapeError(op, "the tensor-core form takes bfloat16")
+    tiles = _moe_tiles(op, sorted_pairs, tile_expert)
+    f = _fn("moe", "vob_moe_gate_up", [_P, _I, _L, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P])
+    _check(f(_ptr(x), _code(x, op), x.stride(0), _ptr(w_gu), _ptr(sorted_pairs), _ptr(tile_expert), tiles, int(top), width, ff,
+             _ptr(h_out), 1 if tensor_cores else 0, _stream()), op)
+
+
+@_timed
+def moe_down(h: torch.Tensor, w_down: torch.Tensor, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, pair_w: torch.Tensor,
+             y: torch.Tensor, tensor_cores: bool = False) -> None:
+    """y[pair] = pair_w[pair] * (W_down[e] h[pair]), float32 [T * top, width]; w_down [E, width, ff] of h's type; pair_w
+    float32 [T, top]."""
+    op = "moe_down"
+    _cuda(op, h, w_down, sorted_pairs, tile_expert, pair_w, y)
+    if h.dim() != 2 or not h.is_contiguous():
+        raise ShapeError(op, f"h must be contiguous [pairs, ff], got {list(h.shape)}")
+    P, ff = h.shape
+    if w_down.dim() != 3 or w_down.shape[2] != ff or w_down.dtype != h.dtype or not w_down.is_contiguous():
+        raise ShapeError(op, f"w_down must be contiguous {h.dtype} [experts, width, {ff}], got {w_down.dtype} {list(w_down.shape)}")
+    width = w_down.shape[1]
+    if pair_w.dtype != torch.float32 or pair_w.numel() != P or not pair_w.is_contiguous():
+        raise ShapeError(op, f"pair_w must be contiguous float32 of {P} entries, got {pair_w.dtype} {list(pair_w.shape)}")
+    if y.dtype != torch.float32 or y.shape != (P, width) or not y.is_contiguous():
+        raise ShapeError(op, f"y must be contiguous float32 [{P}, {width}], got {y.dtype} {list(y.shape)}")
+    if tensor_cores and h.dtype != torch.bfloat16:
+        raise ShapeError(op, "the tensor-core form takes bfloat16")
+    tiles = _moe_tiles(op, sorted_pairs, tile_expert)
+    f = _fn("moe", "vob_moe_down", [_P, _I, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P])
+    _check(f(_ptr(h), _code(h, op), _ptr(w_down), _ptr(sorted_pairs), _ptr(tile_expert), _ptr(pair_w), tiles, width, ff, _ptr(y),
+             1 if tensor_cores else 0, _stream()), op)
+
+
+@_timed
+def moe_combine(y: torch.Tensor, idx: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum over k, in order, of y[t * top + k] where idx[t, k] >= 0; out [T, width] in the activations' type."""
+    op = "moe_combine"
+    _cuda(op, y, idx, out)
+    if idx.dtype != torch.int32 or idx.dim() != 2 or not idx.is_contiguous():
+        raise ShapeError(op, f"idx must be contiguous int32 [T, top], got {idx.dtype} {list(idx.shape)}")
+    T, top = idx.shape
+    if y.dtype != torch.float32 or y.dim() != 2 or y.shape[0] != T * top or not y.is_contiguous():
+        raise ShapeError(op, f"y must be contiguous float32 [{T * top}, width], got {y.dtype} {list(y.shape)}")
+    if out.shape != (T, y.shape[1]) or not out.is_contiguous():
+        raise ShapeError(op, f"out must be contiguous [{T}, {y.shape[1]}], got {list(out.shape)}")
+    f = _fn("moe", "vob_moe_combine", [_P, _P, _I, _I, _I, _P, _I, _P])
+    _check(f(_ptr(y), _ptr(idx), T, top, y.shape[1], _ptr(out), _code(out, op), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention over a latent cache
@@ -1095,24 +1311,35 @@ def _kv_caches(op, kcache, vcache, kv_heads, dim, vdim, dtype):
 @_timed
 def flex_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, positions: torch.Tensor, slots: Optional[torch.Tensor],
               inv_freq: Optional[torch.Tensor], rot: int, unit_rms: bool, eps: float, q_temp, vmix: Optional[torch.Tensor],
-              v_first: Optional[torch.Tensor], v_mode: int, q_out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
-              heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+              v_first: Optional[torch.Tensor], v_mode: int, q_out: torch.Tensor, kcache: Optional[torch.Tensor],
+              vcache: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int,
+              q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None) -> None:
     """Per token, from the columns q_off.., k_off.., v_off.. of `proj`: q and k with their first `rot` features rotated
     (feature i with i + rot / 2, by position * inv_freq[i]), then (unit_rms) divided by sqrt(mean(x^2) + eps) per head;
     q times 1 + coef * ln(floor((pos + 1) / every) + 1) for q_temp = (coef, every). q goes to q_out [T, heads * dim], k
     and v to their cache slots. v_mode 1 also leaves v in v_first [T, kv_heads * vdim]; v_mode 2 mixes
-    v <- (1 - vmix) v + vmix v_first before the write (vmix: one float32 on the device)."""
+    v <- (1 - vmix) v + vmix v_first before the write (vmix: one float32 on the device). `q_norm_w`, `k_norm_w` (float32
+    [dim], shared by the heads) multiply q and k behind the division. Without caches (`kcache` None: a layer that reads
+    what another layer cached) only q is prepared and `proj` needs no k and v columns."""
     op = "flex_prep"
-    _cuda(op, proj, positions, slots, inv_freq, vmix, v_first, q_out, kcache, vcache)
+    _cuda(op, proj, positions, slots, inv_freq, vmix, v_first, q_out, kcache, vcache, q_norm_w, k_norm_w)
     _rows_2d(proj, op, "proj")
     _rows_2d(q_out, op, "q_out")
     T = proj.shape[0]
-    for off, n in ((q_off, heads * dim), (k_off, kv_heads * dim), (v_off, kv_heads * vdim)):
+    if (kcache is None) != (vcache is None):
+        raise ShapeError(op, "both caches or none")
+    spans = ((q_off, heads * dim),) if kcache is None else ((q_off, heads * dim), (k_off, kv_heads * dim), (v_off, kv_heads * vdim))
+    for off, n in spans:
         if off < 0 or off + n > proj.shape[1]:
             raise ShapeError(op, f"columns {off}..{off + n} lie outside proj's {proj.shape[1]}")
     if q_out.shape != (T, heads * dim) or q_out.dtype != proj.dtype:
         raise ShapeError(op, f"q_out must be {proj.dtype} [{T}, {heads * dim}], got {q_out.dtype} {list(q_out.shape)}")
-    _kv_caches(op, kcache, vcache, kv_heads, dim, vdim, proj.dtype)
+    if kcache is not None:
+        _kv_caches(op, kcache, vcache, kv_heads, dim, vdim, proj.dtype)
+    elif v_mode or slots is not None:
+        raise ShapeError(op, "without caches there is nothing to write and no value to mix")
+    _f32_vec(q_norm_w, dim, op, "q_norm_w")
+    _f32_vec(k_norm_w, dim, op, "k_norm_w")
     _int32_vec(positions, T, op, "positions")
     if slots is not None:
         _int32_vec(slots, T, op, "slots")
@@ -1125,24 +1352,32 @@ def flex_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, positions:
     if v_mode == 2:
         _f32_vec(vmix, 1, op, "vmix")
     coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
-    f = _fn("attention_flex", "vob_flex_prep", [_P, _I, _L, _I, _I, _I, _P, _P, _P, _I, _I, _F, _F, _I, _P, _P, _I, _P, _L, _P, _P,
+    f = _fn("attention_flex", "vob_flex_prep", [_P, _I, _L, _I, _I, _I, _P, _P, _P, _I, _I, _F, _F, _I, _P, _P, _P, _P, _I, _P, _L, _P, _P,
                                                 _I, _I, _I, _I, _I, _I, _P])
     _check(f(_ptr(proj), _code(proj, op), proj.stride(0), q_off, k_off, v_off, _ptr(positions), _ptr(slots), _ptr(inv_freq), int(rot),
-             1 if unit_rms else 0, float(eps), coef, every, _ptr(vmix), _ptr(v_first), int(v_mode), _ptr(q_out), q_out.stride(0),
-             _ptr(kcache), _ptr(vcache), T, heads, kv_heads, dim, vdim, kcache.shape[2], _stream()), op)
+             1 if unit_rms else 0, float(eps), coef, every, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(vmix), _ptr(v_first), int(v_mode),
+             _ptr(q_out), q_out.stride(0), _ptr(kcache), _ptr(vcache), T, heads, kv_heads, dim, vdim,
+             kcache.shape[2] if kcache is not None else 1, _stream()), op)
 
 
 @_timed
 def flex_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                    row_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
                    window: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                   out_scale: float = 1.0) -> None:
+                   out_scale: float = 1.0, chunk: int = 0, softcap: float = 0.0, dist_bias=None) -> None:
     """Causal attention of every row of q [T, heads * dim] over its request's pages, keys of `dim` and values of `vdim`
     features: out [T, heads * vdim] (any row stride) = softmax(q . K * scale) V, over the last `window` keys (0: all), the
     denominator also holding exp(sink[head]) if `sink` (float32 [heads]) is given; times sigmoid(gate) ([T, heads * vdim],
-    any row stride) and `out_scale`."""
+    any row stride) and `out_scale`. `chunk` > 0: a query reads only the keys of its own block of `chunk` positions (blocks
+    counted from position 0). `softcap` > 0: score <- softcap * tanh(score / softcap). `dist_bias` = (r1, r2), float32 [heads]
+    each: r1 * ln(1 + r2 * distance) is taken off the score."""
     op = "flex_attention"
-    _cuda(op, q, out, kcache, vcache, block_tables, row_seq, positions, sink, gate)
+    r1, r2 = dist_bias if dist_bias is not None else (None, None)
+    _cuda(op, q, out, kcache, vcache, block_tables, row_seq, positions, sink, gate, r1, r2)
+    _f32_vec(r1, heads, op, "dist_bias[0]")
+    _f32_vec(r2, heads, op, "dist_bias[1]")
+    if chunk < 0 or softcap < 0:
+        raise ShapeError(op, f"chunk {chunk} and softcap {softcap} must not be negative")
     _rows_2d(q, op, "q")
     _rows_2d(out, op, "out")
     T = q.shape[0]
@@ -1164,10 +1399,11 @@ def flex_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vca
         if gate.shape != (T, heads * vdim) or gate.dtype != q.dtype:
             raise ShapeError(op, f"gate must be {q.dtype} [{T}, {heads * vdim}], got {gate.dtype} {list(gate.shape)}")
     f = _fn("attention_flex", "vob_flex_attention", [_P, _L, _P, _L, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P,
-                                                     _L, _F, _P])
+                                                     _L, _F, _I, _F, _P, _P, _P])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _code(q, op), _ptr(block_tables),
              block_tables.shape[1], _ptr(row_seq), _ptr(positions), T, heads, kv_heads, dim, vdim, kcache.shape[2], int(window),
-             float(scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale), _stream()), op)
+             float(scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale), int(chunk),
+             float(softcap), _ptr(r1), _ptr(r2), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention

@@ -5,7 +5,10 @@ from .rotary import Rotary, rotary_inv_freq
 from .attention import Attention
 from .swiglu import SwiGLU
 from .embedding import Embedding, LMHead
-from .block import Block
+from .block import Block, PostNormBlock
+from .layernorm import LayerNorm
+from .mlp import ActMLP
+from .moe import RoutedExperts
 from .streams import PendingWrite, StreamBlock, StreamCoefficients, StreamEmbedding, StreamNorm
 from .recurrent import GatedDelta, GeneralDelta, Retention
 from .flex_attention import SoftmaxAttention
@@ -15,4 +18,5 @@ from .latent_attention import LatentAttention
 __all__ = ["CacheSpec", "PagedTensorSpec", "StateSpec", "LayerCache", "Workspace", "StepContext", "Mixer", "FeedForward", "Norm",
            "PositionEncoding", "LayerCall", "ModelSpec", "FoldedState", "RMSNorm", "Rotary", "rotary_inv_freq", "Attention",
            "SwiGLU", "Embedding", "LMHead", "Block", "PendingWrite", "StreamBlock", "StreamCoefficients", "StreamEmbedding",
-           "StreamNorm", "GeneralDelta", "Retention", "LatentAttention", "GatedDelta", "SoftmaxAttention", "ParallelMixer"]
+           "StreamNorm", "GeneralDelta", "Retention", "LatentAttention", "GatedDelta", "SoftmaxAttention", "ParallelMixer", "PostNormBlock", "LayerNorm",
+           "ActMLP", "RoutedExperts"]

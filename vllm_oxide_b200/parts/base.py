@@ -45,10 +45,12 @@ class CacheSpec:
     """Pages a mixer needs. The mixer says which tensors a page holds: keys and values of
     `num_kv_heads` x `head_dim` (the default, `CacheSpec(kv_heads, head_dim)`), or any other set
     given as `tensors` (one latent vector per token, keys and values of different widths, ...),
-    and whether every token is kept ("full") or only the last `window` ("window")."""
+    and whether every token is kept ("full"), only the last `window` ("window") or only the current block of
+    `window` positions ("chunk")."""
     num_kv_heads: int = 0
     head_dim: int = 0
-    kind: str = "full"          # "full": every key is kept; "window": the last `window` keys
+    kind: str = "full"          # "full": every key is kept; "window": the last `window` keys; "chunk": the keys of
+                                # the query's own block of `window` positions (blocks counted from position 0)
     window: int = 0
     tensors: Tuple[PagedTensorSpec, ...] = ()
 

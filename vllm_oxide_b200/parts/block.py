@@ -1,4 +1,5 @@
-"""The arrangement of parts in one layer: pre-norm residual block.
+"""The arrangements of parts in one layer: the pre-norm residual block (`Block`) and the block whose
+residual takes the normed result of each sub-layer (`PostNormBlock`, at the end of the file).
 
     residual += mixer(norm1(residual));  residual += feed_forward(norm2(residual))
 (crates/engine/src/model.rs:302-332). The residual is float32. Each part's output is not added
@@ -113,3 +114,77 @@ class Block:
             if ff.data_ptr() != out.data_ptr():
                 out.copy_(ff)
         return out
+
+
+class PostNormBlock:
+    """residual += norm1(mixer(residual));  residual += norm2(feed_forward(residual))
+
+    The sub-layers read the residual itself and the norms sit on their results only. The residual is float32; in an
+    engine whose activations are narrower, a sub-layer reads the residual rounded to that type: the kernel that adds a
+    normed result also leaves the new residual in that type, in `out` (which outlives the block), and names it in
+    `ctx.shared[STREAM_COPY]` for the next block of this arrangement, so only the first block of a step runs a kernel
+    that does nothing but round. The norms offer `add_normed(resid, result, copy)` (`LayerNorm`). A block without
+    feed-forward has no second norm. Nothing is left pending: the block returns None."""
+
+    STREAM_COPY = "_residual_in_act_type"
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], feed_forward: Optional[FeedForward]):
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        if (norm2 is None) != (feed_forward is None):
+            raise ValueError("a block has a second norm exactly when it has a feed-forward")
+        for n in (norm1, norm2):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError("the norms of this arrangement must offer add_normed(resid, result, copy)")
+        self.pending_scale = None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def weight_bytes(self) -> int:
+        return sum(getattr(p, "weight_bytes", lambda: 0)() for p in self._parts())
+
+    def workspace_bytes(self, rows: int, hidden: int, act_bytes: int) -> int:
+        """The residual in the activations' type (where that is not float32), one sub-layer's result, and the larger of the
+        two sub-layers' own scratch."""
+        copy = aligned(rows * hidden * act_bytes) if act_bytes != 4 else 0
+        result = aligned(rows * hidden * act_bytes)
+        ff = self.feed_forward.workspace_bytes(rows) if self.feed_forward is not None else 0
+        return 2 * copy + result + max(self.mixer.workspace_bytes(rows), ff)
+
+    def folded_workspace_bytes(self, rows: int) -> int:
+        return 0
+
+    def kernel_modules(self, dtype, max_rows):
+        mods = ["elementwise"]
+        for p in self._parts():
+            mods += list(getattr(p, "kernel_modules", lambda d, r: ())(dtype, max_rows))
+        return tuple(mods)
+
+    def can_fold(self) -> bool:
+        return False
+
+    def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: Optional[LayerCache], state, out: torch.Tensor, pending_scale: Optional[torch.Tensor] = None):
+        if pending is not None:
+            raise ValueError("a block of this arrangement follows blocks that leave nothing pending")
+        from .. import kernels
+        ws = ctx.workspace
+        narrow = ctx.dtype != torch.float32
+        with ws.scope():
+            x = resid
+            if narrow:
+                x = ctx.shared.pop(self.STREAM_COPY, None)
+                if x is None or x.data_ptr() == out.data_ptr():
+                    x = ctx.alloc(resid.shape)
+                    kernels.cast_rows(resid, x)
+            mid = ctx.alloc(resid.shape) if narrow and self.feed_forward is not None else None
+            with ws.scope():
+                m = self.mixer.forward(x, ctx, cache, state)
+                self.norm1.add_normed(resid, m, (mid if self.feed_forward is not None else out) if narrow else None)
+            if self.feed_forward is not None:
+                with ws.scope():
+                    f = self.feed_forward.forward(mid if narrow else resid, ctx)
+                    self.norm2.add_normed(resid, f, out if narrow else None)
+        if narrow:
+            ctx.shared[self.STREAM_COPY] = out
+        return None

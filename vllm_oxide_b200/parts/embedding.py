@@ -12,9 +12,14 @@ from .linear import to_compute
 
 
 class Embedding:
-    def __init__(self, table: torch.Tensor, dtype=torch.bfloat16, device="cuda", scale: float = 1.0):
-        """`scale`: every row is multiplied by it on its way into the float32 residual."""
+    def __init__(self, table: torch.Tensor, dtype=torch.bfloat16, device="cuda", scale: float = 1.0,
+                 positions: torch.Tensor = None):
+        """`scale`: every row is multiplied by it on its way into the float32 residual. `positions` [max positions,
+        hidden]: a learned vector per position, added (not scaled) to the token's row."""
         self.table = to_compute(table, dtype, device)
+        if positions is not None and (positions.dim() != 2 or positions.shape[1] != table.shape[1]):
+            raise ValueError(f"position table {list(positions.shape)} does not fit a width of {table.shape[1]}")
+        self.pos_table = to_compute(positions, dtype, device) if positions is not None else None
         self.scale = float(scale)
         self.vocab, self.hidden = self.table.shape
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=device)
@@ -24,7 +29,8 @@ class Embedding:
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         resid = ctx.alloc((ctx.rows, self.hidden), torch.float32)
-        kernels.embed(self.table, ctx.tokens, resid, self.err_flag, self.scale)
+        kernels.embed(self.table, ctx.tokens, resid, self.err_flag, self.scale, self.pos_table,
+                      ctx.positions if self.pos_table is not None else None)
         return resid
 
     def forward_folded(self, ctx: StepContext, next_norm) -> FoldedState:

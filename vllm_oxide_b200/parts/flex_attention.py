@@ -10,7 +10,16 @@ as parameters:
 * `bias_*`           biases of the q, k, v and output projections;
 * `window`           a query sees itself and the window - 1 tokens before it (pages behind are given back);
 * `rot_dims`, `rot_base`   partial rotary positions, feature i paired with i + rot_dims / 2;
-* `unit_rms_eps`     q and k divided by sqrt(mean(x^2) + eps) per head, after the rotation, no weight;
+* `unit_rms_eps`     q and k divided by sqrt(mean(x^2) + eps) per head, after the rotation;
+* `q_norm_weight`, `k_norm_weight`   [dim] each, shared by the heads: q and k times it behind that division;
+* `chunk`            a query sees only the keys of its own block of `chunk` positions, blocks counted from position 0
+                     (pages of earlier blocks are given back);
+* `softcap`          score <- softcap * tanh(score / softcap);
+* `dist_bias`        (r1, r2), one number per head each: r1 * ln(1 + r2 * (i - j)) is taken off the score of key j;
+* `shared_kv`        the layer has no key and value projections: it reads the cache another layer wrote (the run order
+                     names it: `LayerCall(cache=that layer's, write=False)`), with its own queries, mask and the rest;
+* `cache_keep`       ("full" | "window" | "chunk", size): what the cache keeps where that is more than this layer's own
+                     mask asks for (a cache that layers with different masks read must serve them all);
 * `q_temp`           (coef, every): q times 1 + coef * ln(floor((pos + 1) / every) + 1);
 * `sink`             one number per head whose exponential joins the softmax's denominator (no key, no value);
 * `gate_weight`      the heads' results times sigmoid(W_g x) before the output projection;
@@ -35,18 +44,29 @@ from .rotary import rotary_inv_freq
 
 
 class SoftmaxAttention(Mixer):
-    def __init__(self, wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, wo: torch.Tensor, heads: int, kv_heads: int, dim: int,
+    def __init__(self, wq: torch.Tensor, wk: Optional[torch.Tensor], wv: Optional[torch.Tensor], wo: torch.Tensor, heads: int,
+                 kv_heads: int, dim: int,
                  vdim: int, scale: float, *, bias_q=None, bias_k=None, bias_v=None, bias_o=None, window: int = 0, rot_dims: int = 0,
                  rot_base: float = 10000.0, unit_rms_eps: Optional[float] = None, q_temp: Optional[Tuple[float, int]] = None,
                  sink: Optional[torch.Tensor] = None, gate_weight: Optional[torch.Tensor] = None, value_mix: Optional[str] = None,
-                 mix_weight: Optional[torch.Tensor] = None, shared_name: str = "v_first", dtype=torch.bfloat16, device="cuda"):
+                 mix_weight: Optional[torch.Tensor] = None, shared_name: str = "v_first", q_norm_weight: Optional[torch.Tensor] = None,
+                 k_norm_weight: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0, dist_bias=None,
+                 shared_kv: bool = False, cache_keep: Optional[Tuple[str, int]] = None, dtype=torch.bfloat16, device="cuda"):
         self.H, self.G, self.D, self.DV = int(heads), int(kv_heads), int(dim), int(vdim)
+        self.shared_kv = bool(shared_kv)
+        if self.shared_kv:
+            if wk is not None or wv is not None or bias_k is not None or bias_v is not None or k_norm_weight is not None or value_mix:
+                raise ValueError("a layer that reads another layer's keys and values has no key or value tensors of its own")
+            wk = torch.zeros((0, wq.shape[1]), dtype=wq.dtype, device=wq.device)
+            wv = torch.zeros((0, wq.shape[1]), dtype=wq.dtype, device=wq.device)
         if self.H % self.G:
             raise ValueError(f"{self.H} heads are not a multiple of {self.G} kv heads")
         if self.D > 256 or self.DV > 256:
             raise ValueError(f"head sizes {self.D} / {self.DV} are beyond 256")
         hidden = wq.shape[1]
         nq, nk, nv = self.H * self.D, self.G * self.D, self.G * self.DV
+        if self.shared_kv:
+            nk = nv = 0
         self.n_pre = self.H * self.DV
         if wq.shape != (nq, hidden) or wk.shape != (nk, hidden) or wv.shape != (nv, hidden) or wo.shape != (hidden, self.n_pre):
             raise ValueError(f"projection shapes {list(wq.shape)} / {list(wk.shape)} / {list(wv.shape)} / {list(wo.shape)} do not fit "
@@ -75,6 +95,16 @@ class SoftmaxAttention(Mixer):
             raise ValueError(f"output bias {list(bias_o.shape)} does not fit {hidden}")
         self.b_o = to_compute(bias_o, dtype, device) if bias_o is not None else None
         self.window = int(window) if window else 0
+        self.chunk = int(chunk) if chunk else 0
+        if self.window < 0 or self.chunk < 0 or (self.window and self.chunk):
+            raise ValueError(f"a window of {window} and blocks of {chunk}: one of them at most, none negative")
+        self.softcap = float(softcap) if softcap else 0.0
+        if self.softcap < 0:
+            raise ValueError(f"softcap {softcap} must be positive")
+        own = ("window", self.window) if self.window else ("chunk", self.chunk) if self.chunk else ("full", 0)
+        self.cache_keep = (str(cache_keep[0]), int(cache_keep[1])) if cache_keep is not None else own
+        if self.cache_keep != own and self.cache_keep[0] != "full":
+            raise ValueError(f"a cache that keeps {self.cache_keep} cannot serve a layer that reads {own}")
         self.scale = float(scale)
         self.rot = int(rot_dims)
         if self.rot % 2 or not 0 <= self.rot <= self.D:
@@ -84,6 +114,17 @@ class SoftmaxAttention(Mixer):
         self.eps = float(unit_rms_eps) if self.unit_rms else 0.0
         self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp else None
         f32 = dict(device=device, dtype=torch.float32)
+        for name, nw in (("q_norm_weight", q_norm_weight), ("k_norm_weight", k_norm_weight)):
+            if nw is not None and (nw.shape != (self.D,) or not self.unit_rms):
+                raise ValueError(f"{name} must have {self.D} entries and goes with unit_rms_eps, got {list(nw.shape)}")
+        self.q_norm_w = q_norm_weight.to(**f32).contiguous() if q_norm_weight is not None else None
+        self.k_norm_w = k_norm_weight.to(**f32).contiguous() if k_norm_weight is not None else None
+        self.dist_bias = None
+        if dist_bias is not None:
+            r1, r2 = dist_bias
+            if r1.shape != (self.H,) or r2.shape != (self.H,):
+                raise ValueError(f"the distance bias takes two numbers per head, got {list(r1.shape)} and {list(r2.shape)}")
+            self.dist_bias = (r1.to(**f32).contiguous(), r2.to(**f32).contiguous())
         if sink is not None and sink.shape != (self.H,):
             raise ValueError(f"sink {list(sink.shape)} does not fit {self.H} heads")
         self.sink = sink.to(**f32).contiguous() if sink is not None else None
@@ -102,7 +143,7 @@ class SoftmaxAttention(Mixer):
 
     # ------------------------------------------------------------------ what the runtime asks
     def cache_spec(self) -> Optional[CacheSpec]:
-        return CacheSpec(kind="window" if self.window else "full", window=self.window,
+        return CacheSpec(kind=self.cache_keep[0], window=self.cache_keep[1],
                          tensors=(PagedTensorSpec(self.G, self.D), PagedTensorSpec(self.G, self.DV)))
 
     def shared_buffer(self) -> Optional[Tuple[str, int]]:
@@ -119,9 +160,14 @@ class SoftmaxAttention(Mixer):
         es = self.w_in.element_size()
         return aligned(rows * self.w_in.shape[0] * es) + aligned(rows * self.n_pre * es) + self.core_workspace_bytes(rows)
 
+    def plain_scores(self) -> bool:
+        """Scores that are q . k * scale and nothing else, over all earlier keys or a window: what the framework's
+        tensor-core attention kernels compute."""
+        return not (self.chunk or self.softcap or self.dist_bias is not None)
+
     def tensor_core_sizes(self) -> bool:
         """Keys and values of one size that the framework's tensor-core attention kernels are built for."""
-        return self.D == self.DV and self.D in kernels.TENSOR_CORE_HEAD_DIMS and self.H // self.G <= 16
+        return self.plain_scores() and self.D == self.DV and self.D in kernels.TENSOR_CORE_HEAD_DIMS and self.H // self.G <= 16
 
     def kernel_modules(self, dtype, max_rows):
         if dtype == torch.float32:
@@ -129,7 +175,7 @@ class SoftmaxAttention(Mixer):
         mods = ["gemm_sm100", "attention_flex"]
         if self.tensor_core_sizes():
             mods += ["attention_mma"] + ([] if self.window or self.gated else ["attention_sm100"])
-        elif self.D % 8 == 0 and self.DV % 8 == 0 and self.D <= 128 and self.DV <= 128:
+        elif self.plain_scores() and self.D % 8 == 0 and self.DV % 8 == 0 and self.D <= 128 and self.DV <= 128:
             mods += ["attention_mma"]
         return tuple(mods)
 
@@ -145,9 +191,12 @@ class SoftmaxAttention(Mixer):
         v_first = ctx.shared.get(self.shared_name) if self.v_mode else None
         if self.v_mode and v_first is None:
             raise ValueError(f"the step has no buffer {self.shared_name!r} for the values that layers mix")
+        if self.shared_kv == cache.write:
+            raise ValueError("a layer writes the cache exactly when it has keys and values of its own")
         kernels.flex_prep(proj, self.q_off, self.k_off, self.v_off, ctx.positions, ctx.slot_mapping[cache.group] if cache.write else None,
-                          self.inv_freq, self.rot, self.unit_rms, self.eps, self.q_temp, self.mix_weight, v_first, self.v_mode, q, kc, vc,
-                          self.H, self.G, self.D, self.DV)
+                          self.inv_freq, self.rot, self.unit_rms, self.eps, self.q_temp, self.mix_weight, v_first, self.v_mode, q,
+                          None if self.shared_kv else kc, None if self.shared_kv else vc, self.H, self.G, self.D, self.DV,
+                          self.q_norm_w, self.k_norm_w)
         gate = proj[:, self.g_off:self.g_off + self.n_pre] if self.gated else None
         self.attend(q, pre_out, ctx, cache, gate, out_scale)
 
@@ -180,12 +229,12 @@ class SoftmaxAttention(Mixer):
                                              ctx.max_new, H, G, D, self.scale, self.window, self.sink, gate, out_scale)
                 return
         if (self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0 and not ctx.decode_only and ctx.max_new > 1
-                and kernels.attn_prefill_mma_any_supported(H, G, D, self.DV, page) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
+                and self.plain_scores() and kernels.attn_prefill_mma_any_supported(H, G, D, self.DV, page) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
             kernels.attn_prefill_mma_any(q, out, kc, vc, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs, ctx.max_new, H, G, D, self.DV,
                                          self.scale, self.window, self.sink, gate, out_scale)
             return
         kernels.flex_attention(q, out, kc, vc, bt, ctx.row_seq, ctx.positions, H, G, D, self.DV, self.scale, self.window, self.sink,
-                               gate, out_scale)
+                               gate, out_scale, self.chunk, self.softcap, self.dist_bias)
 
     def _attend_single(self, q, out, ctx: StepContext, cache: LayerCache, bt, count: int, gate, out_scale: float) -> None:
         """The decode kernel on the first `count` rows, row i belonging to request i."""

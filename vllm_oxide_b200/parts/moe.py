@@ -1,0 +1,81 @@
+"""Feed-forward made of many small gated experts of which every token uses a few.
+
+    z = W_router x (float32);  s = softmax(z) over all experts
+    the experts form `groups` runs of neighbours; a run scores as its best expert; only experts of the `keep` best
+    runs can be chosen (no groups: all can);  the `top` experts with the largest s are chosen
+    out = sum over the chosen e of w_e * W_down[e] (silu(W_gate[e] x) * (W_up[e] x)),   w_e = s_e (or s_e / their sum)
+
+Per step: the election (one warp per token), the (token, expert) pairs put in order of their expert on the device
+(no count ever goes to the host, so the step can be recorded in a CUDA graph), one grouped product for gate and up
+with the gate in its epilogue, one for down with the weight in its epilogue, and the sum over a token's choices in
+their own order. bfloat16 engines run the products on the tensor cores (`tensor_cores`), float32 engines as plain
+multiply-add chains over the features in order.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from .. import kernels
+from .base import FeedForward, StepContext, aligned
+from .linear import to_compute
+
+
+class RoutedExperts(FeedForward):
+    def __init__(self, w_router: torch.Tensor, w_gate: Sequence[torch.Tensor], w_up: Sequence[torch.Tensor],
+                 w_down: Sequence[torch.Tensor], top: int, groups: int = 0, keep: int = 0, renormalize: bool = False,
+                 dtype=torch.bfloat16, device="cuda"):
+        E, hidden = w_router.shape
+        if not (len(w_gate) == len(w_up) == len(w_down) == E):
+            raise ValueError(f"the router names {E} experts, got {len(w_gate)} / {len(w_up)} / {len(w_down)} sets of weights")
+        ff = w_gate[0].shape[0]
+        for e in range(E):
+            if w_gate[e].shape != (ff, hidden) or w_up[e].shape != (ff, hidden) or w_down[e].shape != (hidden, ff):
+                raise ValueError(f"expert {e}: shapes {list(w_gate[e].shape)} / {list(w_up[e].shape)} / {list(w_down[e].shape)} do not "
+                                 f"fit {ff} x {hidden}")
+        self.E, self.ff, self.hidden, self.top = E, ff, hidden, int(top)
+        self.groups, self.keep = (int(groups), int(keep)) if groups and groups > 1 else (0, 0)
+        if not 0 < self.top <= E:
+            raise ValueError(f"{top} choices among {E} experts")
+        if self.groups and (E % self.groups or not 0 < self.keep <= self.groups or self.top > self.keep * (E // self.groups)):
+            raise ValueError(f"{E} experts in {groups} groups of which {keep} are kept cannot give {top} choices")
+        self.renorm = bool(renormalize)
+        # the router is float32 whatever the engine computes in
+        self.w_router = w_router.to(device=device, dtype=torch.float32).contiguous()
+        self.w_gu = to_compute(torch.stack([torch.cat([g, u], dim=0) for g, u in zip(w_gate, w_up)]), dtype, device)
+        self.w_down = to_compute(torch.stack(list(w_down)), dtype, device)
+        self.dtype = dtype
+        self.tensor_cores = dtype == torch.bfloat16
+        self.meta = torch.zeros(4, dtype=torch.int32, device=device)
+
+    def weight_bytes(self) -> int:
+        """What a step of one token reads: the router and `top` experts."""
+        es = self.w_down.element_size()
+        return self.w_router.numel() * 4 + self.top * 3 * self.ff * self.hidden * es
+
+    def workspace_bytes(self, rows: int) -> int:
+        es = 2 if self.dtype == torch.bfloat16 else 4
+        P = rows * self.top
+        cap = kernels.moe_sorted_rows(P, self.E)
+        return (2 * aligned(P * 4) + aligned(cap * 4) + aligned(cap // kernels.MOE_TILE_ROWS * 4) + aligned(P * self.ff * es)
+                + aligned(P * self.hidden * 4) + aligned(rows * self.hidden * es))
+
+    def kernel_modules(self, dtype, max_rows):
+        return ("moe",)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, out=None) -> torch.Tensor:
+        T = x.shape[0]
+        P = T * self.top
+        idx, w = ctx.alloc((T, self.top), torch.int32), ctx.alloc((T, self.top), torch.float32)
+        kernels.moe_route(x, self.w_router, ctx.positions, self.top, self.groups, self.keep, self.renorm, idx, w)
+        cap = kernels.moe_sorted_rows(P, self.E)
+        order, tile_expert = ctx.alloc((cap,), torch.int32), ctx.alloc((cap // kernels.MOE_TILE_ROWS,), torch.int32)
+        kernels.moe_align(idx, self.E, order, tile_expert, self.meta)
+        h = ctx.alloc((P, self.ff))
+        kernels.moe_gate_up(x, self.w_gu, order, tile_expert, self.top, h, self.tensor_cores)
+        y = ctx.alloc((P, self.hidden), torch.float32)
+        kernels.moe_down(h, self.w_down, order, tile_expert, w, y, self.tensor_cores)
+        out = out if out is not None else ctx.alloc((T, self.hidden))
+        kernels.moe_combine(y, idx, out)
+        return out

@@ -20,6 +20,8 @@ may share one q and k head):
     beta = sigmoid(W_b h);   g = exp(-exp(A_log_h) softplus(W_a2 W_a1 h + dt_bias))   decay per key channel
     S' = diag(g) S_(t-1);   S_t = S' + k (beta (v - S'^T k))^T;   o = S_t^T q
     out = W_o (rms_head(o) * norm_weight * sigmoid(W_g2 W_g1 h))
+  or, as options: one decay per head, g = exp(-exp(A_log_h) softplus(W_a h + dt_bias_h)) with W_a [heads, width] (no
+  second matrix), and an output gate from one full projection, silu(W_g h) or sigmoid(W_g h).
 Its state is the matrix S and, in a second tensor, the convolutions' last taps - 1 inputs.
 
 All run the same scan kernel (`kernels.recurrence_scan`) for prompt portions and single tokens
@@ -144,14 +146,19 @@ class Retention(Mixer):
 class GatedDelta(Mixer):
     """See the module's head. `conv_q`, `conv_k`, `conv_v` are [channels, taps] with the last column the
     current token's. `w_a1` / `w_a2` and `w_g1` / `w_g2` are the two low-rank pairs (decay and output gate);
+    `w_a2` None: `w_a1` is [heads, width] and gives one decay per head (`dt_bias` [heads]); `w_g2` None: `w_g1` is the
+    full gate projection [heads * vdim, width]; `gate` names the gate's activation ("sigmoid" or "silu").
     `norm_weight` [vdim] is shared by the heads. Like `SoftmaxAttention` it offers its halves separately
     (`w_in`, `core`, `w_o`) for a layer that runs it beside another mixer."""
 
     def __init__(self, wq, wk, wv, conv_q, conv_k, conv_v, wb, a_log, w_a1, w_a2, dt_bias, w_g1, w_g2, norm_weight, wo, heads: int,
-                 kv_heads: int, dim: int, vdim: int, eps: float, dtype=torch.bfloat16, device="cuda"):
+                 kv_heads: int, dim: int, vdim: int, eps: float, dtype=torch.bfloat16, device="cuda", gate: str = "sigmoid"):
         self.H, self.G, self.K, self.V = int(heads), int(kv_heads), int(dim), int(vdim)
         if self.H % self.G:
             raise ValueError(f"{self.H} heads are not a multiple of {self.G} q/k heads")
+        if gate not in ("sigmoid", "silu"):
+            raise ValueError(f"gate {gate!r} is not known (sigmoid or silu)")
+        self.gate = gate
         if self.K > 512:
             raise ValueError(f"a key size of {self.K} is beyond the scan's 512")
         hidden = wq.shape[1]
@@ -163,10 +170,16 @@ class GatedDelta(Mixer):
             if c.shape != (n, self.taps):
                 raise ValueError(f"convolution '{name}' is {list(c.shape)}, expected [{n}, {self.taps}]")
         ra, rg = w_a1.shape[0], w_g1.shape[0]
-        if w_a1.shape != (ra, hidden) or w_a2.shape != (hk, ra) or w_g1.shape != (rg, hidden) or w_g2.shape != (hv, rg):
-            raise ValueError(f"low-rank projections {list(w_a1.shape)} / {list(w_a2.shape)} / {list(w_g1.shape)} / {list(w_g2.shape)} do not fit")
-        if a_log.shape != (self.H,) or dt_bias.shape != (hk,) or norm_weight.shape != (self.V,):
-            raise ValueError("A_log [heads], dt_bias [heads * dim] and the norm weight [vdim] are needed")
+        self.decay_per_head, self.gate_direct = w_a2 is None, w_g2 is None
+        if w_a1.shape != (ra, hidden) or w_g1.shape != (rg, hidden):
+            raise ValueError(f"decay and gate projections {list(w_a1.shape)} / {list(w_g1.shape)} do not read a width of {hidden}")
+        if (self.decay_per_head and ra != self.H) or (not self.decay_per_head and w_a2.shape != (hk, ra)):
+            raise ValueError(f"decay projection {list(w_a1.shape)} fits neither {self.H} heads nor its second matrix")
+        if (self.gate_direct and rg != hv) or (not self.gate_direct and w_g2.shape != (hv, rg)):
+            raise ValueError(f"gate projection {list(w_g1.shape)} fits neither {hv} features nor its second matrix")
+        n_decay = self.H if self.decay_per_head else hk
+        if a_log.shape != (self.H,) or dt_bias.shape != (n_decay,) or norm_weight.shape != (self.V,):
+            raise ValueError(f"A_log [heads], dt_bias [{n_decay}] and the norm weight [vdim] are needed")
         self.C = 2 * gk + hv
         # one matrix [Wq; Wk; Wv; Wa1; Wg1; Wb]: q, k, v side by side (the convolutions' channels), then the
         # two low-rank inputs side by side (one second product serves both), the strengths last
@@ -174,11 +187,20 @@ class GatedDelta(Mixer):
         self.low_off, self.ra, self.rg = self.C, ra, rg
         self.b_off = self.C + ra + rg
         self.b_in = None
-        # [[Wa2, 0], [0, Wg2]]: the zero blocks add exact zeros, so each half is the product of its own pair
-        low = torch.zeros(hk + hv, ra + rg, dtype=torch.float32, device=w_a2.device)
-        low[:hk, :ra] = w_a2.float()
-        low[hk:, ra:] = w_g2.float().to(low.device)
-        self.w_low = to_compute(low, dtype, device)
+        # [[Wa2, 0], [0, Wg2]]: the zero blocks add exact zeros, so each half is the product of its own pair. A half
+        # without a second matrix is read from the first product as it is, and with neither there is no second product.
+        self.w_low = None
+        if not (self.decay_per_head and self.gate_direct):
+            rows_a, rows_g = (0 if self.decay_per_head else hk), (0 if self.gate_direct else hv)
+            cols_a, cols_g = (0 if self.decay_per_head else ra), (0 if self.gate_direct else rg)
+            low = torch.zeros(rows_a + rows_g, cols_a + cols_g, dtype=torch.float32)
+            if not self.decay_per_head:
+                low[:hk, :ra] = w_a2.float().cpu()
+            if not self.gate_direct:
+                low[rows_a:, cols_a:] = w_g2.float().cpu()
+            self.w_low = to_compute(low, dtype, device)
+            if self.decay_per_head != self.gate_direct:
+                raise ValueError("the decay and the gate are both low-rank pairs or both single projections")
         self.w_o = to_compute(wo, dtype, device)
         self.b_o = None
         self.n_pre = hv
@@ -193,7 +215,8 @@ class GatedDelta(Mixer):
         return (s, StateSpec((self.taps - 1, self.C), torch.float32)) if self.taps > 1 else (s,)
 
     def weight_bytes(self) -> int:
-        return (self.w_in.numel() + self.w_low.numel() + self.w_o.numel()) * self.w_in.element_size()
+        low = self.w_low.numel() if self.w_low is not None else 0
+        return (self.w_in.numel() + low + self.w_o.numel()) * self.w_in.element_size()
 
     def core_workspace_bytes(self, rows: int) -> int:
         es, gk, hk, hv = self.w_in.element_size(), self.G * self.K, self.H * self.K, self.H * self.V
@@ -213,18 +236,24 @@ class GatedDelta(Mixer):
             raise ValueError("the gated delta rule needs its state")
         S, conv_state = state[0], (state[1] if self.taps > 1 else None)
         T, gk, hk, hv = proj.shape[0], self.G * self.K, self.H * self.K, self.H * self.V
-        low = ctx.alloc((T, hk + hv))
-        kernels.linear(proj[:, self.low_off:self.low_off + self.ra + self.rg], self.w_low, low)
+        if self.w_low is not None:
+            low = ctx.alloc((T, hk + hv))
+            kernels.linear(proj[:, self.low_off:self.low_off + self.ra + self.rg], self.w_low, low)
+            a_src, a_off, g_src = low, 0, low[:, hk:]
+        else:       # [.. | W_a h (heads) | W_g h (heads * vdim) | ..] are columns of the first product
+            a_src, a_off = proj, self.low_off
+            g_src = proj[:, self.low_off + self.ra:self.low_off + self.ra + self.rg]
         q, k = ctx.alloc((T, gk), torch.float32), ctx.alloc((T, gk), torch.float32)
         v = ctx.alloc((T, hv))
         decay, strength = ctx.alloc((T, hk), torch.float32), ctx.alloc((T, self.H), torch.float32)
-        kernels.gated_delta_prep(proj, 0, self.b_off, low, 0, self.conv_w, conv_state, self.a_log, self.dt_bias, ctx.positions, ctx.row_seq,
-                                 ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, self.G, self.K, self.V, q, k, v, decay, strength)
+        kernels.gated_delta_prep(proj, 0, self.b_off, a_src, a_off, self.conv_w, conv_state, self.a_log, self.dt_bias, ctx.positions,
+                                 ctx.row_seq, ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, self.G, self.K, self.V, q, k, v, decay,
+                                 strength, self.decay_per_head)
         o = ctx.alloc((T, hv), torch.float32)
         # the scan also leaves the convolutions' last inputs in the request's slot (the preparation has read the old ones)
         kernels.recurrence_scan(2, q, k, v, decay, strength, None, S, ctx.seq_starts, ctx.state_slots, ctx.seqs, self.H, o, rk_heads=self.G,
                                 conv_x=proj[:, :self.C] if conv_state is not None else None, conv_state=conv_state)
-        kernels.recurrence_post(o, low[:, hk:], self.norm_weight, "sigmoid", self.eps, self.H, pre_out, out_scale)
+        kernels.recurrence_post(o, g_src, self.norm_weight, self.gate, self.eps, self.H, pre_out, out_scale)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state, out=None) -> torch.Tensor:
         T = x.shape[0]
