@@ -924,6 +924,144 @@ def lomopel_compare(a):
     return 0
 
 
+# Layer sizes at which the Bufulorn design is measured beside Lomopel, the closest design the engine has (attention with
+# options, a gated delta rule), at the same width, feed-forward, layer count, attention heads and delta-rule sizes (those of
+# LOMOPEL_SIZES): the length of a block of positions, and the routed experts (all experts together as large as the dense
+# feed-forward, a token using two of them).
+BUFULORN_SIZES = {
+    "1b": dict(lomopel="1b", chunk=1536, softcap=30.0, moe=dict(ff=1024, experts=8, top=2, groups=4, keep=2)),
+    "3b": dict(lomopel="3b", chunk=1536, softcap=30.0, moe=dict(ff=1024, experts=8, top=2, groups=4, keep=2)),
+}
+
+
+def make_bufulorn_engine(bs, blocks, max_seqs, tokens_per_request, context):
+    """(config, LLM): `blocks` times the four layers [attention + dense, delta rule + experts, attention that reads the
+    first layer's keys and values + dense, delta rule + dense], random weights drawn on the device."""
+    import torch
+    from vllm_oxide_b200 import models
+    from vllm_oxide_b200.config import (BufulornConfig, BufulornLayer, ChunkAttentionConfig, EngineConfig, FeedForwardConfig,
+                                        HeadDecayDeltaConfig)
+    from vllm_oxide_b200.engine import LLM, ModelRunner
+    from vllm_oxide_b200.weights import random_tensors
+    ls = LOMOPEL_SIZES[bs["lomopel"]]
+    at, d = ls["attn"], ls["delta"]
+    dense = FeedForwardConfig("dense", ls["ff"])
+    moe = FeedForwardConfig("moe", **bs["moe"])
+    delta = HeadDecayDeltaConfig(heads=d["heads"], kv_heads=d["kv_heads"], dim=d["dim"], vdim=d["vdim"], conv=d["conv"])
+    layers = []
+    for b in range(blocks):
+        own = ChunkAttentionConfig(scale=at["dim"] ** -0.5, softcap=bs["softcap"], chunk=bs["chunk"], **at)
+        reader = ChunkAttentionConfig(scale=at["dim"] ** -0.5, softcap=bs["softcap"], chunk=bs["chunk"], kv_from=4 * b, **at)
+        layers += [BufulornLayer("attention", attention=own, mlp=dense), BufulornLayer("delta", delta=delta, mlp=moe),
+                   BufulornLayer("attention", attention=reader, mlp=dense), BufulornLayer("delta", delta=delta, mlp=dense)]
+    cfg = BufulornConfig(vocab=128256, width=ls["width"], norm_eps=1e-5, max_positions=context, layers=tuple(layers))
+    pages_per_req = -(-(tokens_per_request + 16) // 16)
+    fields = dict(max_batch_tokens=2048, max_seqs=max_seqs, max_model_len=context, block_size=16,
+                  num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=True)
+    fields.update(ENGINE_OVERRIDES)
+    tensors = random_tensors(models.bufulorn_manifest(cfg), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
+    runner = ModelRunner(cfg, tensors, EngineConfig(**fields))
+    del tensors
+    return cfg, LLM(runner)
+
+
+def bufulorn_roofline(bs, blocks, n, batch, peaks, prefill, decode):
+    """The design's own kernels against their rooflines: algorithmic bytes (or FLOPs) of all their launches in one step
+    over the measured time, as a fraction of the measured copy bandwidth (or the measured bfloat16 product rate)."""
+    ls = LOMOPEL_SIZES[bs["lomopel"]]
+    at, d, W, F, chunk, m = ls["attn"], ls["delta"], ls["width"], ls["ff"], bs["chunk"], bs["moe"]
+    out = {}
+
+    def add(names, label, phase, totals, nbytes=None, flops=None):
+        ms = sum(t for op, _, t in totals if op in names)
+        if ms <= 0:
+            return
+        e = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / ms / 1e6, 1)
+            e["of_measured_hbm"] = round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 2)
+            e["of_measured_bf16"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        out[f"{phase}:{label}"] = e
+    qd, kd, vd = at["heads"] * at["dim"], at["kv_heads"] * at["dim"], at["kv_heads"] * at["vdim"]
+    for phase, rows, totals in (("prefill", n, prefill), ("decode", batch, decode)):
+        # every sub-layer: the result read, the float32 residual read and written, its rounding written
+        add(("layernorm_add",), "layernorm_add", phase, totals, nbytes=8 * blocks * rows * W * (2 + 2 * 4 + 2))
+        # keys a row reads: those of its own block of positions that are not behind it
+        if phase == "prefill":
+            keys = sum(i % chunk + 1 for i in range(n))
+        else:
+            keys = batch * ((n + 2) % chunk + 1)
+        fl = 2 * blocks * keys * at["heads"] * 2 * (at["dim"] + at["vdim"])
+        by = 2 * blocks * keys * (kd + vd) * 2 if phase == "decode" else None
+        add(("flex_attention", "attn_prefill_mma_any", "attn_prefill_mma", "attn_decode_mma"), "attention", phase, totals, nbytes=by, flops=fl)
+        # a layer with keys of its own: q, k, v read, q written, k and v written to the cache; a reader: q read and written
+        add(("flex_prep",), "flex_prep", phase, totals, nbytes=blocks * rows * ((2 * qd + 2 * kd + 2 * vd) + 2 * qd) * 2)
+        seqs = 1 if phase == "prefill" else batch
+        H, K, V, G = d["heads"], d["dim"], d["vdim"], d["kv_heads"]
+        state = 2 * blocks * H * K * V * 4 * 2 * seqs
+        per_token = 2 * blocks * (2 * G * K * 4 + H * V * 2 + H * 4 * 2 + H * V * 4)
+        add(("recurrence_scan",), "recurrence_scan", phase, totals, nbytes=state + rows * per_token,
+            flops=2 * blocks * rows * 2 * H * K * V * 4)
+        C = 2 * G * K + H * V
+        add(("gated_delta_prep", "conv_state_update"), "gated_delta_prep", phase, totals,
+            nbytes=2 * blocks * rows * (C * 2 + 2 * H * 2 + 2 * G * K * 4 + H * V * 2 + 2 * H * 4))
+        add(("recurrence_post",), "recurrence_post", phase, totals, nbytes=2 * blocks * rows * H * V * (4 + 2 + 2))
+        # the activation between the two products of a dense feed-forward: read and written in place
+        add(("activation",), "xielu", phase, totals, nbytes=3 * blocks * rows * F * 2 * 2)
+        # routed experts: the weights of every expert that is used are read once (decode), 3 products of ff x width a choice
+        P, used = rows * m["top"], min(m["experts"], rows * m["top"])
+        add(("moe_gate_up", "moe_down"), "expert products", phase, totals,
+            nbytes=blocks * (used * 3 * m["ff"] * W * 2 + P * (W * 2 + 2 * m["ff"] * 2 + W * 4)), flops=blocks * P * 3 * 2 * m["ff"] * W)
+        add(("moe_route", "moe_align", "moe_combine"), "election, order, sum", phase, totals,
+            nbytes=blocks * (rows * W * 2 + m["experts"] * W * 4 + P * W * 4 + rows * W * 2))
+    return out
+
+
+def bufulorn_compare(a):
+    """Prefill and decode of the Bufulorn design beside Lomopel of the same width, feed-forward, layer count, attention
+    heads and delta-rule sizes; one JSON line. Device-timed like the benchmark's own points: one step of 2,048 prompt
+    tokens (median of 5 after 3), decode steps replayed from CUDA graphs (`--steps` steps a region, median region)."""
+    import torch
+    peaks = load_peaks()
+    n, B, blocks = 2048, a.batch, 2
+    gen = a.warmup + max(a.steps, MAX_TIMED_STEPS) + 64
+    sampler = ClockSampler()
+    sampler.start()
+    points = []
+    for key in a.bufulorn.split(","):
+        bs = BUFULORN_SIZES[key]
+        ls = LOMOPEL_SIZES[bs["lomopel"]]
+        point = {"sizes": key, "layers": 4 * blocks, "prompt_len": n, "batch": B}
+        for arch in ("bufulorn", "lomopel"):
+            if arch == "bufulorn":
+                cfg, llm = make_bufulorn_engine(bs, blocks, B, n + gen, 8192)
+            else:
+                cfg, llm = make_lomopel_engine(ls, blocks, B, n + gen, 8192)
+            g = torch.Generator().manual_seed(1)
+            prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for _ in range(B)]
+            ms_prefill = timed_prefill(llm, prompts[0], n)
+            ms_step, ctx_tokens, launches, regions = decode_device(llm, prompts, B, a.steps, a.warmup, n, gen)
+            prefill, decode = op_profile(llm, prompts, n, B)
+            e = {"prefill_tok_s": round(n / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                 "decode_tok_s": round(B / ms_step * 1e3, 1), "decode_ms_per_step": round(ms_step, 4),
+                 "decode_hbm_frac_of_measured": round(llm.runner.step_read_bytes(int(ctx_tokens)) / ms_step / 1e6 / peaks["hbm_gbs"], 3),
+                 "launches_per_decode_step": launches // a.steps,
+                 "ops_prefill_ms": {op: round(t, 4) for op, _, t in prefill}, "ops_decode_ms": {op: round(t, 4) for op, _, t in decode}}
+            e["kernels"] = bufulorn_roofline(bs, blocks, n, B, peaks, prefill, decode) if arch == "bufulorn" else \
+                lomopel_roofline(ls, blocks, n, B, peaks, prefill, decode)
+            point[arch] = e
+            free_engine(llm)
+            del llm
+        points.append(point)
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "Bufulorn beside Lomopel at equal width, feed-forward, layer count, attention heads and delta-rule sizes: "
+                                "prefill and decode tok/s",
+                      "dtype": "bf16", "data": "synthetic", "peaks": peaks, "points": points, "clocks": clocks, "run": run_record()}))
+    return 0
+
+
 def main():
     if "--kernel" in sys.argv[1:]:
         return kernel_case(sys.argv[1:])
@@ -956,6 +1094,9 @@ def main():
     ap.add_argument("--lomopel", default=None, metavar="SIZES", const="1b,3b", nargs="?",
                     help="instead of the benchmark's line: the Lomopel design beside Llama at equal sizes (1b, 3b or both), "
                          "prefill and decode, with the time and roofline fraction of every kernel")
+    ap.add_argument("--bufulorn", default=None, metavar="SIZES", const="1b,3b", nargs="?",
+                    help="instead of the benchmark's line: the Bufulorn design beside Lomopel at equal sizes (1b, 3b or both), "
+                         "prefill and decode, with the time and roofline fraction of every kernel")
     ap.add_argument("--tuning", action="append", default=[], metavar="FIELD=VALUE",
                     help="set a field of vllm_oxide_b200.tuning.TUNING (experiments)")
     ap.add_argument("--fold-rows", type=int, default=None, metavar="R",
@@ -978,6 +1119,8 @@ def main():
         return rotepel_compare(a)
     if a.lomopel:
         return lomopel_compare(a)
+    if a.bufulorn:
+        return bufulorn_compare(a)
     prompt_len, gen_len = a.prompt_len, a.gen_len
     max_b = max(a.batch, 1 if (a.no_points or a.serve or a.timeline) else 64)
     if a.serve:

@@ -74,6 +74,50 @@ __device__ __forceinline__ float tail_val(const AttnTail& t, long long row, int 
     return v;
 }
 
+// What may lie between q . k and the softmax (all optional; the kernels built with SHAPED take it):
+//   chunk > 0    a query reads only the keys of its own block of `chunk` positions, blocks counted from position 0;
+//   a cap        score <- softcap * tanh(score / softcap);
+//   r1, r2       [H] each: r1 * ln(1 + r2 * (i - j)) is taken off the score of key j for the query at i.
+// Scores leave in base-2 units (times log2 e), and the launchers' scale_log2 is not used by a shaped kernel. The struct
+// is a kernel parameter: what the inner loop reads of it comes from the constant bank and holds no register.
+struct ScoreShape {
+    int chunk;
+    float pre;            // q . k times this is tanh's argument (scale / softcap); without a cap, the score in base-2 units
+    float cap_log2;       // softcap * log2 e, 0: no cap
+    const float* r1;
+    const float* r2;
+};
+inline ScoreShape make_shape(int chunk, float softcap, const float* r1, const float* r2, float scale) {
+    const float log2e = 1.4426950408889634f;
+    return ScoreShape{chunk, softcap > 0.f ? scale / softcap : scale * log2e, softcap > 0.f ? softcap * log2e : 0.f, r1, r2};
+}
+// The distance bias of a thread's two rows: r1 and r2 of their heads (zero for a row that is no row of the request).
+struct RowShape {
+    float r1[2], r2[2];
+};
+__device__ __forceinline__ RowShape row_shape(const ScoreShape& sh, int head0, int head1) {
+    RowShape rs;
+    const bool bias = sh.r1 != nullptr;
+    rs.r1[0] = bias && head0 >= 0 ? sh.r1[head0] : 0.f;
+    rs.r1[1] = bias && head1 >= 0 ? sh.r1[head1] : 0.f;
+    rs.r2[0] = bias && head0 >= 0 ? sh.r2[head0] : 0.f;
+    rs.r2[1] = bias && head1 >= 0 ? sh.r2[head1] : 0.f;
+    return rs;
+}
+// The first key a query at `pos` reads (0 for a row of position -1, which is no row of a request).
+__device__ __forceinline__ int first_key(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos + 1 - window) : 0;
+    return chunk > 0 ? max(lo, pos - pos % chunk) : lo;
+}
+// tanh from one exponential and one division: absolute error of a few 1e-7 (the argument is clamped where
+// tanh is 1 to float32's last place), which a capped score of some tens keeps far below one bfloat16 step of q . k.
+__device__ __forceinline__ float fast_tanh(float x) {
+    x = fminf(fmaxf(x, -15.f), 15.f);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.885390081777927f));
+    return 1.f - __fdividef(2.f, e + 1.f);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -149,18 +193,28 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const uint32_t (&
 
 // Mask, running maximum, exponentials; returns P as A-fragments. s holds NB n-blocks of 8 keys
 // starting at key index key0; this thread's rows are r and r+8 with limits [lo, pos]. With MASK
-// false the caller knows that every key of the tile is visible to every row of the warp.
-template <int NB, int HDN, bool MASK>
+// false the caller knows that every key of the tile is visible to every row of the warp. SHAPED: the scores
+// first become what `rs` makes of them (cap, distance bias), in base-2 units, and `scale_log2` is not used.
+template <int NB, int HDN, bool MASK, bool SHAPED = false>
 __device__ __forceinline__ void softmax_step(float (&s)[NB][4], uint32_t (&pa)[NB / 2][4], float (&o)[HDN][4],
                                              float (&m)[2], float (&l)[2], int key0, const int (&lo)[2],
-                                             const int (&pos)[2], float scale_log2) {
+                                             const int (&pos)[2], float scale_log2, const ScoreShape* sh = nullptr,
+                                             const RowShape* rs = nullptr) {
     int lane = threadIdx.x & 31;
     float mx[2] = {-INFINITY, -INFINITY};
+    if (SHAPED) scale_log2 = 1.f;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             int h = i >> 1;
+            if (SHAPED) {
+                int j = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
+                float t = s[nb][i] * sh->pre;
+                if (sh->cap_log2 > 0.f) t = sh->cap_log2 * fast_tanh(t);
+                if (sh->r1) t -= rs->r1[h] * __log2f(fmaf(rs->r2[h], (float)max(pos[h] - j, 0), 1.f));
+                s[nb][i] = t;
+            }
             if (MASK) {
                 int j = key0 + nb * 8 + (lane & 3) * 2 + (i & 1);
                 if (!(j >= lo[h] && j <= pos[h])) s[nb][i] = -INFINITY;
@@ -362,13 +416,13 @@ __device__ __forceinline__ void load_rows_padded(__nv_bfloat16* dst, const __nv_
     }
 }
 
-template <int HD, int HDV>
+template <int HD, int HDV, bool SHAPED>
 __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
                             long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                             const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
                             const int* __restrict__ context_lens, int H, int KV, int D, int DV, int page_shift, int window,
-                            float scale_log2, AttnTail tail) {
+                            float scale_log2, AttnTail tail, ScoreShape shape) {
     constexpr int LD = HD + 8, LDV = HDV + 8;
     constexpr int BM = 64;
     pdl_launch_dependents();
@@ -404,7 +458,8 @@ attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
     const int last_rr = min(tile_row0 + BM, total_rows) - 1;
     const int hi = ctx + last_rr / G + 1;
     const int first_tok_pos = ctx + tile_row0 / G;
-    const int lo_blk = window > 0 ? max(0, first_tok_pos + 1 - window) : 0;
+    const int chunk = SHAPED ? shape.chunk : 0;
+    const int lo_blk = first_key(first_tok_pos, window, chunk);      // the block's first row reads furthest back
     const int t_begin = lo_blk / BN, t_end = (hi + BN - 1) / BN;
     const int page0 = lo_blk >> page_shift, page_end = ((hi - 1) >> page_shift) + 1;
     for (int i = threadIdx.x; i < page_end - page0; i += NTHREADS) s_pages[i] = bt[page0 + i];
@@ -414,19 +469,25 @@ attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
     load_rows_padded<HDV>(sV0, vc, DV, s_pages, page0, kvh, KV, page_shift, t_begin * BN, lo_blk, hi);
     cp_async_commit();
 
-    int pos[2], lo[2];
+    int pos[2], lo[2], hd[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         int rr = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
         pos[h] = rr < total_rows ? ctx + rr / G : -1;
-        lo[h] = window > 0 ? max(0, pos[h] + 1 - window) : 0;
+        hd[h] = rr < total_rows ? kvh * G + rr % G : -1;
+        lo[h] = first_key(pos[h], window, chunk);
     }
+    RowShape rs;
+    if (SHAPED) rs = row_shape(shape, hd[0], hd[1]);
     int warp_last_pos = max(pos[0], pos[1]), warp_first_pos = min(pos[0], pos[1]), warp_max_lo = max(lo[0], lo[1]);
+    int warp_min_lo = 0;                             // blocks of positions: the first key any row of the warp reads
+    if (SHAPED) warp_min_lo = min(pos[0] < 0 ? 0x7fffffff : lo[0], pos[1] < 0 ? 0x7fffffff : lo[1]);
 #pragma unroll
     for (int x = 4; x < 32; x <<= 1) {
         warp_last_pos = max(warp_last_pos, __shfl_xor_sync(0xffffffffu, warp_last_pos, x));
         warp_first_pos = min(warp_first_pos, __shfl_xor_sync(0xffffffffu, warp_first_pos, x));
         warp_max_lo = max(warp_max_lo, __shfl_xor_sync(0xffffffffu, warp_max_lo, x));
+        if (SHAPED) warp_min_lo = min(warp_min_lo, __shfl_xor_sync(0xffffffffu, warp_min_lo, x));
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[HDV / 8][4];
@@ -452,14 +513,15 @@ attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
             for (int kk = 0; kk < HD / 16; ++kk)
                 ldmatrix_x4(qf[kk], sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
         }
-        if (t * BN <= warp_last_pos) {
+        // nor has one whose rows all begin to read behind this tile's last key
+        if (t * BN <= warp_last_pos && (!SHAPED || (t + 1) * BN > warp_min_lo)) {
             float s[8][4];
             qk_tile<HD, 8>(s, qf, sK, 0);
             uint32_t pa[4][4];
             if ((t + 1) * BN - 1 <= warp_first_pos && t * BN >= warp_max_lo)
-                softmax_step<8, HDV / 8, false>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
+                softmax_step<8, HDV / 8, false, SHAPED>(s, pa, o, m, l, t * BN, lo, pos, scale_log2, &shape, &rs);
             else
-                softmax_step<8, HDV / 8, true>(s, pa, o, m, l, t * BN, lo, pos, scale_log2);
+                softmax_step<8, HDV / 8, true, SHAPED>(s, pa, o, m, l, t * BN, lo, pos, scale_log2, &shape, &rs);
             pv_tile<HDV, 4>(o, pa, sV, 0);
         }
     }
@@ -568,13 +630,13 @@ template <int HD, int DEC_STAGES> __host__ __device__ constexpr size_t decode_ri
 }
 __host__ __device__ constexpr size_t decode_recv_bytes(int G, int HD) { return (size_t)(G * HD + 8 + 256) * sizeof(float); }
 
-template <int HD, int DEC_STAGES>
+template <int HD, int DEC_STAGES, bool SHAPED>
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, __nv_bfloat16* __restrict__ out,
                        long long out_stride, const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc,
                        const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
                        int H, int KV, int page_shift, int window, float scale_log2, float* __restrict__ partials,
-                       int* __restrict__ arrived, AttnTail tail) {
+                       int* __restrict__ arrived, AttnTail tail, ScoreShape shape) {
     constexpr int LD = HD + 8;
     constexpr int PART = 16 * HD + 32;                                          // floats of one block's partial
     pdl_launch_dependents();
@@ -603,7 +665,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* bt = block_tables + (size_t)seq * max_pages;
     const int hi = p + 1;
-    const int lo_key = (p >= 0 && window > 0) ? max(0, p + 1 - window) : 0;
+    const int lo_key = first_key(p, window, SHAPED ? shape.chunk : 0);
     const int t_first = lo_key / BN;
     const int n_tiles = p >= 0 ? (hi + BN - 1) / BN - t_first : 0;
     if (partials) {
@@ -660,6 +722,11 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
         pos[h] = r < G ? p : -1;
         lo[h] = lo_key;
     }
+    RowShape rs;
+    if (SHAPED) {
+        const int r0 = lane >> 2;
+        rs = row_shape(shape, r0 < G ? kvh * G + r0 : -1, r0 + 8 < G ? kvh * G + r0 + 8 : -1);
+    }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[HD / 8][4];
 #pragma unroll
@@ -689,7 +756,7 @@ attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, 
         float s[2][4];
         qk_tile<HD, 2>(s, qf, sK, warp * 2);                    // this warp's 16 keys of the tile
         uint32_t pa[1][4];
-        softmax_step<2, HD / 8, true>(s, pa, o, m, l, t * BN + warp * 16, lo, pos, scale_log2);
+        softmax_step<2, HD / 8, true, SHAPED>(s, pa, o, m, l, t * BN + warp * 16, lo, pos, scale_log2, &shape, &rs);
         pv_tile<HD, 1>(o, pa, sV, warp);
     }
     cp_async_wait<0>();
@@ -837,10 +904,10 @@ int launch_prefill(const void* q, long long q_stride, void* out, long long out_s
         scale * 1.4426950408889634f, tail);
 }
 
-template <int HD, int ST>
+template <int HD, int ST, bool SHAPED>
 int launch_decode_st(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                      const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                     float scale, int splits, float* partials, int* arrived, AttnTail tail, cudaStream_t stream) {
+                     float scale, int splits, float* partials, int* arrived, AttnTail tail, ScoreShape shape, cudaStream_t stream) {
     static size_t configured = 0;
     // a block's page list: its share of the tiles of the longest request the block table can hold
     // (a request with few tiles uses fewer blocks, but then the tiles are few)
@@ -849,7 +916,7 @@ int launch_decode_st(const void* q, long long q_stride, void* out, long long out
     if (partials && per_max < 2 * DEC_MIN_TILES) per_max = 2 * DEC_MIN_TILES;
     long long pages_cta = per_max * (BN / page_size) + 1;
     size_t smem = decode_smem<HD, ST>(H / KV, splits > 1 && !partials) + (size_t)pages_cta * sizeof(int);
-    int e = ensure_smem(attn_decode_mma_kernel<HD, ST>, smem, &configured);
+    int e = ensure_smem(attn_decode_mma_kernel<HD, ST, SHAPED>, smem, &configured);
     if (e) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S, KV, splits);
@@ -865,16 +932,16 @@ int launch_decode_st(const void* q, long long q_stride, void* out, long long out
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_vob_pdl ? 2 : 1;
-    cudaError_t ce = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, ST>, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
+    cudaError_t ce = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, ST, SHAPED>, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out,
                                         out_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, bt, max_pages, positions,
-                                        H, KV, log2_exact(page_size), window, scale * 1.4426950408889634f, partials, arrived, tail);
+                                        H, KV, log2_exact(page_size), window, scale * 1.4426950408889634f, partials, arrived, tail, shape);
     return ce != cudaSuccess ? (int)ce : vob_launch_status();
 }
 
-template <int HD>
+template <int HD, bool SHAPED>
 int launch_decode(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                   const int* bt, int max_pages, const int* positions, int S, int H, int KV, int page_size, int window,
-                  float scale, int splits, float* partials, int* arrived, AttnTail tail, cudaStream_t stream) {
+                  float scale, int splits, float* partials, int* arrived, AttnTail tail, ScoreShape shape, cudaStream_t stream) {
     static int num_sms = 0;
     if (!num_sms) {
         int dev = 0;
@@ -886,31 +953,58 @@ int launch_decode(const void* q, long long q_stride, void* out, long long out_st
     long long blocks = (long long)S * KV * splits;
     long long fit3 = (long long)num_sms * ((227 * 1024) / (long long)(decode_smem<HD, 3>(H / KV, splits > 1 && !partials) + 2048));
     if (blocks <= fit3)
-        return launch_decode_st<HD, 3>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
-                                       window, scale, splits, partials, arrived, tail, stream);
-    return launch_decode_st<HD, 2>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
-                                   window, scale, splits, partials, arrived, tail, stream);
+        return launch_decode_st<HD, 3, SHAPED>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
+                                               window, scale, splits, partials, arrived, tail, shape, stream);
+    return launch_decode_st<HD, 2, SHAPED>(q, q_stride, out, out_stride, kc, vc, bt, max_pages, positions, S, H, KV, page_size,
+                                           window, scale, splits, partials, arrived, tail, shape, stream);
 }
 
-template <int HD, int HDV>
+template <int HD, int HDV, bool SHAPED>
 int launch_prefill_any(const void* q, long long q_stride, void* out, long long out_stride, const void* kc, const void* vc,
                        const int* bt, int max_pages, const int* seq_starts, const int* context_lens, int S, int max_new,
-                       int H, int KV, int D, int DV, int page_size, int window, float scale, AttnTail tail, cudaStream_t stream) {
+                       int H, int KV, int D, int DV, int page_size, int window, float scale, AttnTail tail, ScoreShape shape,
+                       cudaStream_t stream) {
     static size_t configured = 0;
     size_t smem = ((size_t)(64 + 2 * BN) * (HD + 8) + (size_t)2 * BN * (HDV + 8)) * sizeof(__nv_bfloat16) + (size_t)max_pages * sizeof(int);
-    int e = ensure_smem(attn_prefill_mma_any_kernel<HD, HDV>, smem, &configured);
+    int e = ensure_smem(attn_prefill_mma_any_kernel<HD, HDV, SHAPED>, smem, &configured);
     if (e) return e;
     const long long row_tiles = ((long long)max_new * (H / KV) + 63) / 64;
     if (row_tiles > 65535) return VOB_ERR_UNSUPPORTED;
     dim3 grid(KV, S, (unsigned)row_tiles);
-    return vob_launch(attn_prefill_mma_any_kernel<HD, HDV>, grid, dim3(NTHREADS), smem, stream,
+    return vob_launch(attn_prefill_mma_any_kernel<HD, HDV, SHAPED>, grid, dim3(NTHREADS), smem, stream,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, bt, max_pages, seq_starts, context_lens, H, KV, D, DV, log2_exact(page_size), window,
-        scale * 1.4426950408889634f, tail);
+        scale * 1.4426950408889634f, tail, shape);
 }
 
 bool sizes_ok(int H, int KV, int hd, int page_size) {
     return (hd == 64 || hd == 128) && KV > 0 && H % KV == 0 && page_size > 0 && BN % page_size == 0;
+}
+
+// The checks and the choice of tile widths of the portion kernel for keys and values of sizes of their own.
+template <bool SHAPED>
+int prefill_any(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache, const void* vcache,
+                const int* block_tables, int max_pages, const int* seq_starts, const int* context_lens, int S, int max_new, int H,
+                int KV, int D, int DV, int page_size, int window, float scale, AttnTail tail, ScoreShape shape, cudaStream_t stream) {
+    if (S <= 0 || max_new <= 0) return 0;
+    if (KV <= 0 || H % KV != 0 || page_size <= 0 || BN % page_size != 0) return VOB_ERR_UNSUPPORTED;
+    if (D <= 0 || DV <= 0 || D % 8 != 0 || DV % 8 != 0 || D > 128 || DV > 128) return VOB_ERR_UNSUPPORTED;
+    if (q_stride % 8 != 0 || out_stride % 2 != 0 || S > 65535 || KV > 65535) return VOB_ERR_BAD_ARG;
+#define VOB_ANY(HD_, HDV_)                                                                                                          \
+    return launch_prefill_any<HD_, HDV_, SHAPED>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,  \
+                                                 context_lens, S, max_new, H, KV, D, DV, page_size, window, scale, tail, shape, stream)
+#define VOB_ANY_V(HD_)                                                                                                              \
+    do {                                                                                                                            \
+        if (DV <= 32) VOB_ANY(HD_, 32);                                                                                             \
+        if (DV <= 64) VOB_ANY(HD_, 64);                                                                                             \
+        VOB_ANY(HD_, 128);                                                                                                          \
+    } while (0)
+    if (D <= 32) VOB_ANY_V(32);
+    if (D <= 64) VOB_ANY_V(64);
+    if (D <= 96) VOB_ANY_V(96);
+    VOB_ANY_V(128);
+#undef VOB_ANY_V
+#undef VOB_ANY
 }
 
 }  // namespace
@@ -944,26 +1038,25 @@ VOB_EXPORT int vob_attn_prefill_mma_any(const void* q, long long q_stride, void*
                                         const int* context_lens, int S, int max_new, int H, int KV, int D, int DV, int page_size,
                                         int window, float scale, const float* sink, const void* gate, long long gate_stride,
                                         float out_scale, cudaStream_t stream) {
-    if (S <= 0 || max_new <= 0) return 0;
-    if (KV <= 0 || H % KV != 0 || page_size <= 0 || BN % page_size != 0) return VOB_ERR_UNSUPPORTED;
-    if (D <= 0 || DV <= 0 || D % 8 != 0 || DV % 8 != 0 || D > 128 || DV > 128) return VOB_ERR_UNSUPPORTED;
-    if (q_stride % 8 != 0 || out_stride % 2 != 0 || S > 65535 || KV > 65535) return VOB_ERR_BAD_ARG;
     const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
-#define VOB_ANY(HD_, HDV_)                                                                                                          \
-    return launch_prefill_any<HD_, HDV_>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts,          \
-                                         context_lens, S, max_new, H, KV, D, DV, page_size, window, scale, tail, stream)
-#define VOB_ANY_V(HD_)                                                                                                              \
-    do {                                                                                                                            \
-        if (DV <= 32) VOB_ANY(HD_, 32);                                                                                             \
-        if (DV <= 64) VOB_ANY(HD_, 64);                                                                                             \
-        VOB_ANY(HD_, 128);                                                                                                          \
-    } while (0)
-    if (D <= 32) VOB_ANY_V(32);
-    if (D <= 64) VOB_ANY_V(64);
-    if (D <= 96) VOB_ANY_V(96);
-    VOB_ANY_V(128);
-#undef VOB_ANY_V
-#undef VOB_ANY
+    return prefill_any<false>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts, context_lens, S, max_new,
+                              H, KV, D, DV, page_size, window, scale, tail, make_shape(0, 0.f, nullptr, nullptr, scale), stream);
+}
+
+// The same with scores that are shaped before the softmax: a query reads the keys of its own block of `chunk` positions
+// (0: no blocks), score <- softcap * tanh(score / softcap) (0: no cap), r1[head] * ln(1 + r2[head] * distance) is taken
+// off (r1, r2 float32 [H], or both null). Any sign of `scale`.
+VOB_EXPORT int vob_attn_prefill_shaped(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
+                                       const void* vcache, const int* block_tables, int max_pages, const int* seq_starts,
+                                       const int* context_lens, int S, int max_new, int H, int KV, int D, int DV, int page_size,
+                                       int window, float scale, const float* sink, const void* gate, long long gate_stride,
+                                       float out_scale, int chunk, float softcap, const float* r1, const float* r2,
+                                       cudaStream_t stream) {
+    const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
+    if (chunk < 0 || softcap < 0.f || (r1 != nullptr) != (r2 != nullptr)) return VOB_ERR_BAD_ARG;
+    const ScoreShape shape = make_shape(chunk, softcap, r1, r2, scale);
+    return prefill_any<true>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts, context_lens, S, max_new,
+                             H, KV, D, DV, page_size, window, scale, tail, shape, stream);
 }
 
 // `splits` (1..8) blocks share each (request, kv head) as one cluster. With `partials` (float32
@@ -975,12 +1068,33 @@ VOB_EXPORT int vob_attn_decode_mma(const void* q, long long q_stride, void* out,
                                    void* partials, int* arrived, const float* sink, const void* gate, long long gate_stride,
                                    float out_scale, cudaStream_t stream) {
     const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
+    const ScoreShape none = make_shape(0, 0.f, nullptr, nullptr, scale);
     if (S <= 0) return 0;
     if (!sizes_ok(H, KV, hd, page_size) || H / KV > 16) return VOB_ERR_UNSUPPORTED;
     if ((partials == nullptr) != (arrived == nullptr)) return VOB_ERR_BAD_ARG;
     if (q_stride % 8 != 0 || splits < 1 || splits > (partials ? DEC_MAX_SPLITS_WIDE : 8) || KV > 65535) return VOB_ERR_BAD_ARG;
-    if (hd == 64) return launch_decode<64>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S,
-                                          H, KV, page_size, window, scale, splits, (float*)partials, arrived, tail, stream);
-    return launch_decode<128>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S, H, KV,
-                              page_size, window, scale, splits, (float*)partials, arrived, tail, stream);
+    if (hd == 64) return launch_decode<64, false>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S,
+                                                 H, KV, page_size, window, scale, splits, (float*)partials, arrived, tail, none, stream);
+    return launch_decode<128, false>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S, H, KV,
+                                     page_size, window, scale, splits, (float*)partials, arrived, tail, none, stream);
+}
+
+// vob_attn_decode_mma with shaped scores (see vob_attn_prefill_shaped).
+VOB_EXPORT int vob_attn_decode_shaped(const void* q, long long q_stride, void* out, long long out_stride, const void* kcache,
+                                      const void* vcache, const int* block_tables, int max_pages, const int* positions, int S,
+                                      int H, int KV, int hd, int page_size, int window, float scale, int splits,
+                                      void* partials, int* arrived, const float* sink, const void* gate, long long gate_stride,
+                                      float out_scale, int chunk, float softcap, const float* r1, const float* r2,
+                                      cudaStream_t stream) {
+    const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
+    if (S <= 0) return 0;
+    if (chunk < 0 || softcap < 0.f || (r1 != nullptr) != (r2 != nullptr)) return VOB_ERR_BAD_ARG;
+    const ScoreShape shape = make_shape(chunk, softcap, r1, r2, scale);
+    if (!sizes_ok(H, KV, hd, page_size) || H / KV > 16) return VOB_ERR_UNSUPPORTED;
+    if ((partials == nullptr) != (arrived == nullptr)) return VOB_ERR_BAD_ARG;
+    if (q_stride % 8 != 0 || splits < 1 || splits > (partials ? DEC_MAX_SPLITS_WIDE : 8) || KV > 65535) return VOB_ERR_BAD_ARG;
+    if (hd == 64) return launch_decode<64, true>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S,
+                                                H, KV, page_size, window, scale, splits, (float*)partials, arrived, tail, shape, stream);
+    return launch_decode<128, true>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, positions, S, H, KV,
+                                    page_size, window, scale, splits, (float*)partials, arrived, tail, shape, stream);
 }

@@ -1464,6 +1464,21 @@ def _attn_tail(op, q, sink, gate, num_heads, out_scale):
     return _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale)
 
 
+def _score_shape(op, q, num_heads, chunk, softcap, dist_bias):
+    """Checked arguments of what may shape a score before the softmax, or None where there is nothing: blocks of `chunk`
+    positions (a query reads its own block's keys only), score <- softcap * tanh(score / softcap), and dist_bias = (r1, r2),
+    float32 [H] each: r1 * ln(1 + r2 * distance) taken off."""
+    if not chunk and not softcap and dist_bias is None:
+        return None
+    if chunk < 0 or softcap < 0:
+        raise ShapeError(op, f"blocks of {chunk} and a cap of {softcap} must not be negative")
+    r1, r2 = dist_bias if dist_bias is not None else (None, None)
+    _cuda(op, q, r1, r2)
+    _f32_vec(r1, num_heads, op, "dist_bias[0]")
+    _f32_vec(r2, num_heads, op, "dist_bias[1]")
+    return int(chunk), float(softcap), _ptr(r1), _ptr(r2)
+
+
 def _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim):
     _cuda(op, q, out, kcache, vcache, block_tables)
     _rows_2d(q, op, "q")
@@ -1520,13 +1535,14 @@ def attn_prefill_mma_any_supported(num_heads: int, num_kv_heads: int, dim: int, 
 @_timed
 def attn_prefill_mma_any(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
                          num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0, sink=None, gate=None,
-                         out_scale: float = 1.0) -> None:
+                         out_scale: float = 1.0, chunk: int = 0, softcap: float = 0.0, dist_bias=None) -> None:
     """Tensor-core attention for portions of prompts and mixed batches (bfloat16) with keys of `dim` and values of `vdim`
     features: q [T, H * dim], out [T, H * vdim] (any row stride), kcache [pages, KV, page, dim], vcache [pages, KV, page, vdim].
     The tiles in shared memory are padded with zero columns to the sizes the kernel is built for. Everything else as
-    `attn_prefill_mma`."""
+    `attn_prefill_mma`. `chunk`, `softcap`, `dist_bias`: see `_score_shape` (the kernel built for shaped scores runs then)."""
     op = "attn_prefill_mma_any"
-    if not scale > 0:
+    shape = _score_shape(op, q, num_heads, chunk, softcap, dist_bias)
+    if shape is None and not scale > 0:
         raise ShapeError(op, f"the score scale must be positive, got {scale}")
     _cuda(op, q, out, kcache, vcache, block_tables, seq_starts, context_lens)
     _rows_2d(q, op, "q")
@@ -1551,12 +1567,15 @@ def attn_prefill_mma_any(q, out, kcache, vcache, block_tables, seq_starts, conte
         _rows_2d(gate, op, "gate")
         if gate.shape != out.shape or gate.dtype != torch.bfloat16:
             raise ShapeError(op, f"gate must be bfloat16 {list(out.shape)}, got {gate.dtype} {list(gate.shape)}")
-    f = _fn("attention_mma", "vob_attn_prefill_mma_any",
-            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _L, _F, _P])
-    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
-             block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads, num_kv_heads,
-             dim, vdim, kcache.shape[2], int(window), float(scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
-             float(out_scale), _stream()), op)
+    sig = [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _L, _F]
+    args = (_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+            block_tables.shape[1], _ptr(seq_starts), _ptr(context_lens), num_seqs, max_new, num_heads, num_kv_heads,
+            dim, vdim, kcache.shape[2], int(window), float(scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+            float(out_scale))
+    if shape is None:
+        _check(_fn("attention_mma", "vob_attn_prefill_mma_any", sig + [_P])(*args, _stream()), op)
+    else:
+        _check(_fn("attention_mma", "vob_attn_prefill_shaped", sig + [_I, _F, _P, _P, _P])(*args, *shape, _stream()), op)
 
 
 def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_pages: int) -> bool:
@@ -1614,8 +1633,8 @@ def attn_prefill_sm100(q, out, kcache, vcache, block_tables, seq_starts, context
 @_timed
 def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: int = 0, splits: int = 1, partials=None, arrived=None, sink=None, gate=None,
-                    out_scale: float = 1.0) -> None:
-    """`sink`, `gate`, `out_scale`: see `_attn_tail`.
+                    out_scale: float = 1.0, chunk: int = 0, softcap: float = 0.0, dist_bias=None) -> None:
+    """`sink`, `gate`, `out_scale`: see `_attn_tail`; `chunk`, `softcap`, `dist_bias`: see `_score_shape`.
     Tensor-core attention for a step of single tokens, row i belonging to request i (bfloat16).
     With splits > 1 (at most 8) each request's keys are shared out over the blocks of a cluster,
     which merge their partial results through distributed shared memory. With `partials` (float32,
@@ -1623,7 +1642,8 @@ def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: 
     the kernel leaves them zero) up to 64 blocks share a request without a cluster and merge
     through global memory: for few requests with long contexts."""
     op = "attn_decode_mma"
-    if not scale > 0:
+    shape = _score_shape(op, q, num_heads, chunk, softcap, dist_bias)
+    if shape is None and not scale > 0:
         raise ShapeError(op, f"the score scale must be positive, got {scale}")
     _attn_common_checks(op, q, out, kcache, vcache, block_tables, num_heads, num_kv_heads, head_dim)
     _cuda(op, positions)
@@ -1646,11 +1666,14 @@ def attn_decode_mma(q, out, kcache, vcache, block_tables, positions, num_heads: 
         if arrived.dtype != torch.int32 or not arrived.is_contiguous() or arrived.numel() < S * num_kv_heads:
             raise ShapeError(op, f"arrived must be contiguous int32 with at least {S * num_kv_heads} elements")
     tail = _attn_tail(op, q, sink, gate, num_heads, out_scale)
-    f = _fn("attention_mma", "vob_attn_decode_mma",
-            [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _P, _L, _F, _P])
-    _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
-             block_tables.shape[1], _ptr(positions), S, num_heads, num_kv_heads, head_dim, kcache.shape[2], int(window),
-             float(scale), int(splits), _ptr(partials), _ptr(arrived), *tail, _stream()), op)
+    sig = [_P, _L, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _P, _L, _F]
+    args = (_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(block_tables),
+            block_tables.shape[1], _ptr(positions), S, num_heads, num_kv_heads, head_dim, kcache.shape[2], int(window),
+            float(scale), int(splits), _ptr(partials), _ptr(arrived), *tail)
+    if shape is None:
+        _check(_fn("attention_mma", "vob_attn_decode_mma", sig + [_P])(*args, _stream()), op)
+    else:
+        _check(_fn("attention_mma", "vob_attn_decode_shaped", sig + [_I, _F, _P, _P, _P])(*args, *shape, _stream()), op)
 
 
 def attn_decode_partial_floats(num_seqs: int, num_kv_heads: int, head_dim: int, splits: int) -> int:

@@ -169,13 +169,25 @@ class SoftmaxAttention(Mixer):
         """Keys and values of one size that the framework's tensor-core attention kernels are built for."""
         return self.plain_scores() and self.D == self.DV and self.D in kernels.TENSOR_CORE_HEAD_DIMS and self.H // self.G <= 16
 
+    def shape_args(self) -> dict:
+        """What shapes this layer's scores before the softmax, as the kernels' keyword arguments."""
+        return dict(chunk=self.chunk, softcap=self.softcap, dist_bias=self.dist_bias)
+
+    def padded_tile_sizes(self) -> bool:
+        """Keys and values of sizes the portion kernel with padded tiles takes."""
+        return self.D % 8 == 0 and self.DV % 8 == 0 and self.D <= 128 and self.DV <= 128
+
+    def shaped_decode_sizes(self) -> bool:
+        """Shaped scores with keys and values of one size the split-key decode kernel is built for."""
+        return not self.plain_scores() and self.D == self.DV and self.D in kernels.TENSOR_CORE_HEAD_DIMS and self.H // self.G <= 16
+
     def kernel_modules(self, dtype, max_rows):
         if dtype == torch.float32:
             return ("gemm_f32", "attention_flex")
         mods = ["gemm_sm100", "attention_flex"]
         if self.tensor_core_sizes():
             mods += ["attention_mma"] + ([] if self.window or self.gated else ["attention_sm100"])
-        elif self.plain_scores() and self.D % 8 == 0 and self.DV % 8 == 0 and self.D <= 128 and self.DV <= 128:
+        elif self.padded_tile_sizes():
             mods += ["attention_mma"]
         return tuple(mods)
 
@@ -206,8 +218,11 @@ class SoftmaxAttention(Mixer):
         mma.sync one, each of which ends with this mixer's sink, gate and factor; a mixed step's leading single tokens
         go to the decode kernel and the portions behind them to the portion kernel. bfloat16 with keys and values of
         other sizes (multiples of 8 up to 128 each, different or not): portions and mixed steps go to the mma.sync
-        portion kernel that pads its tiles, steps of single tokens to the general kernel. Everything else (float32,
-        other sizes) goes to the general kernel."""
+        portion kernel that pads its tiles, steps of single tokens to the general kernel. Scores that are shaped
+        before the softmax (blocks of positions, a cap, a distance bias) take the same two mma.sync kernels in their
+        shaped build: the padded portion kernel for portions and mixed steps of any of those sizes, the split-key
+        decode kernel for steps of single tokens with keys and values of one size of 64 or 128. Everything else
+        (float32, other sizes) goes to the general kernel."""
         kc, vc = cache.tensors[0], cache.tensors[1]
         page, bt = kc.shape[2], ctx.block_tables[cache.group]
         H, G, D = self.H, self.G, self.D
@@ -228,24 +243,30 @@ class SoftmaxAttention(Mixer):
                     kernels.attn_prefill_mma(q, out, kc, vc, bt[lead:], ctx.seq_starts[lead:], ctx.context_lens[lead:], ctx.seqs - lead,
                                              ctx.max_new, H, G, D, self.scale, self.window, self.sink, gate, out_scale)
                 return
-        if (self.dtype == torch.bfloat16 and self.impl != "general" and self.scale > 0 and not ctx.decode_only and ctx.max_new > 1
-                and self.plain_scores() and kernels.attn_prefill_mma_any_supported(H, G, D, self.DV, page) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
+        shaped = not self.plain_scores()
+        if (self.dtype == torch.bfloat16 and self.impl != "general" and shaped and ctx.decode_only and self.shaped_decode_sizes()
+                and kernels.attn_mma_supported(H, G, D, page, True) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
+            self._attend_single(q, out, ctx, cache, bt, ctx.rows, gate, out_scale)
+            return
+        if (self.dtype == torch.bfloat16 and self.impl != "general" and (self.scale > 0 or shaped) and not ctx.decode_only and ctx.max_new > 1
+                and kernels.attn_prefill_mma_any_supported(H, G, D, self.DV, page) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
             kernels.attn_prefill_mma_any(q, out, kc, vc, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs, ctx.max_new, H, G, D, self.DV,
-                                         self.scale, self.window, self.sink, gate, out_scale)
+                                         self.scale, self.window, self.sink, gate, out_scale, **self.shape_args())
             return
         kernels.flex_attention(q, out, kc, vc, bt, ctx.row_seq, ctx.positions, H, G, D, self.DV, self.scale, self.window, self.sink,
                                gate, out_scale, self.chunk, self.softcap, self.dist_bias)
 
     def _attend_single(self, q, out, ctx: StepContext, cache: LayerCache, bt, count: int, gate, out_scale: float) -> None:
         """The decode kernel on the first `count` rows, row i belonging to request i."""
-        splits, wide = decode_split_rule(count, self.G, self.num_sms, ctx.long_context and not self.window)
+        splits, wide = decode_split_rule(count, self.G, self.num_sms, ctx.long_context and not self.window and not self.chunk)
         if wide and self._partials is None:
             floats = kernels.attn_decode_partial_floats(1, 1, self.D, 3 * self.num_sms)    # requests x kv heads x splits <= 3 SMs
             self._partials = torch.empty(floats, dtype=torch.float32, device=q.device)
             self._arrived = torch.zeros(self.num_sms, dtype=torch.int32, device=q.device)
         kernels.attn_decode_mma(q[:count], out[:count], cache.tensors[0], cache.tensors[1], bt, ctx.positions[:count], self.H, self.G,
                                 self.D, self.scale, self.window, splits, self._partials if wide else None,
-                                self._arrived if wide else None, self.sink, gate[:count] if gate is not None else None, out_scale)
+                                self._arrived if wide else None, self.sink, gate[:count] if gate is not None else None, out_scale,
+                                **self.shape_args())
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state=None, out=None) -> torch.Tensor:
         T = x.shape[0]
