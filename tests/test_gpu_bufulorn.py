@@ -538,10 +538,12 @@ def test_election_among_the_best_groups():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,width,ff,E,top,groups,keep", [(1, 48, 24, 8, 2, 4, 3), (37, 42, 20, 5, 1, 0, 0), (300, 64, 16, 6, 3, 2, 2),
-                                                          (70, 96, 96, 12, 3, 3, 2), (5, 40, 136, 16, 4, 4, 2)])
+                                                          (70, 96, 96, 12, 3, 3, 2), (5, 40, 136, 16, 4, 4, 2), (700, 72, 104, 4, 2, 0, 0),
+                                                          (9, 2048, 72, 6, 2, 3, 2)])
 def test_routed_experts_against_every_expert_done_plainly(dtype, T, width, ff, E, top, groups, keep):
     """Election, ordering by expert, both grouped products and the weighted sum, with an expert nobody chooses and rows
-    of padding, against the plain sum over all experts."""
+    of padding, against the plain sum over all experts. In bfloat16 with rows that 16-byte copies can fetch, tiles of
+    128 pairs give bit for bit what tiles of 32 give."""
     from vllm_oxide_b200 import kernels
     torch.manual_seed(T + E)
     x = torch.randn(T, width).to(dtype)
@@ -557,20 +559,27 @@ def test_routed_experts_against_every_expert_done_plainly(dtype, T, width, ff, E
     idx, w = torch.empty(T, top, dtype=torch.int32, device=DEV), torch.empty(T, top, device=DEV)
     kernels.moe_route(xd, wr.to(DEV), pos.to(DEV), top, groups, keep, False, idx, w)
     P = T * top
-    cap = kernels.moe_sorted_rows(P, E)
-    order = torch.empty(cap, dtype=torch.int32, device=DEV)
-    tile_expert = torch.empty(cap // kernels.MOE_TILE_ROWS, dtype=torch.int32, device=DEV)
-    meta = torch.zeros(4, dtype=torch.int32, device=DEV)
-    kernels.moe_align(idx, E, order, tile_expert, meta)
-    listed = sorted(p for p in order.tolist() if p >= 0)
-    assert listed == [p for p in range(P) if int(idx.reshape(-1)[p]) >= 0]     # every live pair once
     tc = dtype == torch.bfloat16
-    h = torch.empty(P, ff, dtype=dtype, device=DEV)
-    kernels.moe_gate_up(xd, torch.cat([wg, wu], 1).contiguous().to(DEV), order, tile_expert, top, h, tc)
-    y = torch.empty(P, width, device=DEV)
-    kernels.moe_down(h, wd.to(DEV), order, tile_expert, w, y, tc)
-    out = torch.empty(T, width, dtype=dtype, device=DEV)
-    kernels.moe_combine(y, idx, out)
+    outs = []
+    for tile in (kernels.MOE_TILE_ROWS, kernels.MOE_LARGE_TILE_ROWS):
+        if tile != kernels.MOE_TILE_ROWS and not (tc and width % 8 == 0 and ff % 8 == 0):
+            continue
+        cap = kernels.moe_sorted_rows(P, E, tile)
+        order = torch.empty(cap, dtype=torch.int32, device=DEV)
+        tile_expert = torch.empty(cap // tile, dtype=torch.int32, device=DEV)
+        meta = torch.zeros(4, dtype=torch.int32, device=DEV)
+        kernels.moe_align(idx, E, order, tile_expert, meta, tile)
+        listed = sorted(p for p in order.tolist() if p >= 0)
+        assert listed == [p for p in range(P) if int(idx.reshape(-1)[p]) >= 0]     # every live pair once
+        h = torch.full((P, ff), float("nan"), dtype=dtype, device=DEV)
+        kernels.moe_gate_up(xd, torch.cat([wg, wu], 1).contiguous().to(DEV), order, tile_expert, top, h, tc, tile)
+        y = torch.full((P, width), float("nan"), device=DEV)
+        kernels.moe_down(h, wd.to(DEV), order, tile_expert, w, y, tc, tile)
+        out = torch.empty(T, width, dtype=dtype, device=DEV)
+        kernels.moe_combine(y, idx, out)
+        outs.append(out)
+    if len(outs) == 2:
+        assert torch.equal(outs[0], outs[1])
     t = {"router": wr.double()}
     for e in range(E):
         t[f"e{e}.gate"], t[f"e{e}.up"], t[f"e{e}.down"] = wg[e].double(), wu[e].double(), wd[e].double()

@@ -23,7 +23,7 @@ VOB_PDL_SWITCH(moe)
 #define VOB_MOE_BM 32
 
 // ---------------------------------------------------------------------------------------------
-// Routing. One warp per token, four tokens per block; E floats of shared memory per warp.
+// Routing. Four tokens per block, one warp per token for the election; 2 E floats of shared memory per token.
 // Rows with a negative position (padding) choose nothing: their indices are -1.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -35,6 +35,20 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
+template <typename T> __device__ __forceinline__ void moe_ld4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void moe_ld4<float>(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+template <> __device__ __forceinline__ void moe_ld4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 a = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&a.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
+    v[0] = __bfloat162float(lo.x); v[1] = __bfloat162float(lo.y); v[2] = __bfloat162float(hi.x); v[3] = __bfloat162float(hi.y);
+}
+
+// The block's four warps first share out the experts: a warp reads an expert's router row once and multiplies it with
+// the rows of all four tokens (a lane's chain runs over its own features in order, whoever the other tokens are; rows
+// whose width and addresses allow are read four features at a time). Then warp w holds the election of token w.
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ x, long ld_x, const float* __restrict__ w_router, const int* __restrict__ positions,
@@ -44,7 +58,41 @@ moe_route_kernel(const T* __restrict__ x, long ld_x, const float* __restrict__ w
     pdl_wait(71);
     extern __shared__ float sc_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
+    const int t0 = blockIdx.x * 4;
+    const T* rows[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) rows[k] = x + (size_t)min(t0 + k, T_rows - 1) * ld_x;
+    const bool by4 = width % 4 == 0 && ld_x % 4 == 0 && (((uintptr_t)x) & (4 * sizeof(T) - 1)) == 0 && (((uintptr_t)w_router) & 15) == 0;
+    for (int e = warp; e < E; e += 4) {
+        const float* wr = w_router + (size_t)e * width;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (by4) {
+#pragma unroll 2
+            for (int i = lane * 4; i < width; i += 128) {
+                const float4 w4 = *reinterpret_cast<const float4*>(wr + i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float v[4];
+                    moe_ld4<T>(rows[k] + i, v);
+                    acc[k] = fmaf(v[0], w4.x, acc[k]); acc[k] = fmaf(v[1], w4.y, acc[k]);
+                    acc[k] = fmaf(v[2], w4.z, acc[k]); acc[k] = fmaf(v[3], w4.w, acc[k]);
+                }
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) {
+                const float w1 = wr[i];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = fmaf(ld_f(rows[k] + i), w1, acc[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float total = warp_sum(acc[k]);
+            if (lane == 0) sc_all[(size_t)k * 2 * E + e] = total;
+        }
+    }
+    __syncthreads();
+    const int t = t0 + warp;
     if (t >= T_rows) return;
     if (positions && positions[t] < 0) {
         for (int k = lane; k < top; k += 32) { idx_out[(size_t)t * top + k] = -1; w_out[(size_t)t * top + k] = 0.f; }
@@ -52,14 +100,6 @@ moe_route_kernel(const T* __restrict__ x, long ld_x, const float* __restrict__ w
     }
     float* sc = sc_all + (size_t)warp * 2 * E;       // scores, then the working copy the election strikes names from
     float* cand = sc + E;
-    const T* xr = x + (size_t)t * ld_x;
-    for (int e = 0; e < E; ++e) {
-        const float* wr = w_router + (size_t)e * width;
-        float acc = 0.f;
-        for (int i = lane; i < width; i += 32) acc = fmaf(ld_f(xr + i), wr[i], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) sc[e] = acc;
-    }
     __syncwarp();
     float m = -INFINITY;
     for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
@@ -128,14 +168,15 @@ VOB_EXPORT int vob_moe_route(const void* x, int code, long ld_x, const float* w_
 
 // ---------------------------------------------------------------------------------------------
 // Ordering. One block of 1024 threads. idx [P] (P = tokens * top; -1: no pair) ->
-//   sorted [cap]: pair numbers expert by expert, each expert's run padded with -1 to a multiple of VOB_MOE_BM;
-//   tile_expert [cap / VOB_MOE_BM]: the expert of every tile (-1 behind the last one);  meta[0] = tiles in use.
-// cap >= P rounded up + E * VOB_MOE_BM. Where a pair lands inside its expert's run is decided by atomics and may
+//   sorted [cap]: pair numbers expert by expert, each expert's run padded with -1 to a multiple of the tile's rows
+//   (32, or 128 for the large tiles of the pipelined products);
+//   tile_expert [cap / rows]: the expert of every tile (-1 behind the last one);  meta[0] = tiles in use.
+// cap >= P rounded up + E * rows. Where a pair lands inside its expert's run is decided by atomics and may
 // differ from run to run; no result depends on it.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ sorted, int cap, int* __restrict__ tile_expert,
-                 int* __restrict__ meta) {
+                 int* __restrict__ meta, int bm) {
     pdl_launch_dependents();
     pdl_wait(72);
     extern __shared__ int sh[];
@@ -153,18 +194,18 @@ moe_align_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ so
         int at = 0;
         for (int e = 0; e < E; ++e) {
             start[e] = at;
-            at += (count[e] + VOB_MOE_BM - 1) / VOB_MOE_BM * VOB_MOE_BM;
+            at += (count[e] + bm - 1) / bm * bm;
         }
         start[E] = at;
-        meta[0] = at / VOB_MOE_BM;
+        meta[0] = at / bm;
     }
     __syncthreads();
     const int used = start[E];
     for (int i = threadIdx.x; i < cap; i += blockDim.x) sorted[i] = -1;
-    for (int i = threadIdx.x; i < cap / VOB_MOE_BM; i += blockDim.x) tile_expert[i] = -1;
+    for (int i = threadIdx.x; i < cap / bm; i += blockDim.x) tile_expert[i] = -1;
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x)
-        for (int tl = start[e] / VOB_MOE_BM; tl < start[e + 1] / VOB_MOE_BM; ++tl) tile_expert[tl] = e;
+        for (int tl = start[e] / bm; tl < start[e + 1] / bm; ++tl) tile_expert[tl] = e;
     for (int p = threadIdx.x; p < P; p += blockDim.x) {
         const int e = idx[p];
         if (e >= 0 && e < E) sorted[start[e] + atomicAdd(&cursor[e], 1)] = p;
@@ -172,12 +213,14 @@ moe_align_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ so
     (void)used;
 }
 
-VOB_EXPORT int vob_moe_align(const int* idx, int P, int E, int* sorted, int cap, int* tile_expert, int* meta, cudaStream_t stream) {
+VOB_EXPORT int vob_moe_align(const int* idx, int P, int E, int* sorted, int cap, int* tile_expert, int* meta, int tile_rows, cudaStream_t stream) {
+    const int bm = tile_rows;
+    if (bm != VOB_MOE_BM && bm != 128) return VOB_ERR_BAD_ARG;
     if (P <= 0) return 0;
-    if (E <= 0 || cap % VOB_MOE_BM != 0 || cap < (P + VOB_MOE_BM - 1) / VOB_MOE_BM * VOB_MOE_BM + E * VOB_MOE_BM) return VOB_ERR_BAD_ARG;
+    if (E <= 0 || cap % bm != 0 || cap < (P + bm - 1) / bm * bm + E * bm) return VOB_ERR_BAD_ARG;
     const size_t smem = (size_t)(3 * E + 1) * sizeof(int);
     if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
-    return vob_launch(moe_align_kernel, dim3(1), dim3(1024), smem, stream, idx, P, E, sorted, cap, tile_expert, meta);
+    return vob_launch(moe_align_kernel, dim3(1), dim3(1024), smem, stream, idx, P, E, sorted, cap, tile_expert, meta, bm);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -466,17 +509,176 @@ moe_down_tc_kernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __r
     }
 }
 
-// `tensor_cores` (bfloat16 only): the wmma form. `max_tiles` = rows of `sorted` / VOB_MOE_BM: the grid covers them all and
-// tiles behind the last one in use leave at once.
+// ---------------------------------------------------------------------------------------------
+// The same two products for rows that 16-byte copies can fetch (K a multiple of 8, 16-byte aligned rows): tiles of BM
+// pairs (32: four warps; 128: eight warps, two along the rows) and 128 weight rows (gate_up: 64 gate and the 64 up rows
+// of the same hidden columns; down: 128 output columns), 32 features a stage, STAGES stages in flight through cp.async
+// (absent rows and features behind K arrive as zeros). The order of a sum is the one of the kernels above: 16
+// features a step, in order.
+// ---------------------------------------------------------------------------------------------
+#define VOB_MOE_PK 32
+#define VOB_MOE_PLD (VOB_MOE_PK + 8)
+
+__device__ __forceinline__ void moe_cp16(void* dst, const void* src, int bytes) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void moe_cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void moe_cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <int BM, int STAGES, bool DOWN>
+__global__ void __launch_bounds__(BM == 128 ? 256 : 128)
+moe_pipe_kernel(const __nv_bfloat16* __restrict__ a, long ld_a, int a_div, const __nv_bfloat16* __restrict__ w,
+                const int* __restrict__ sorted, const int* __restrict__ tile_expert, const float* __restrict__ pair_w,
+                int K, int N, void* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait(DOWN ? 76 : 75);
+    constexpr int WR = BM == 128 ? 2 : 1;             // warps along the rows
+    constexpr int NT = 128 * WR;
+    constexpr int RF = BM / WR / 16;                   // 16-row fragments a warp owns
+    constexpr int ROWS = BM + 128;                     // rows of a stage: the pairs, then the weight rows
+    constexpr int CHUNKS = (ROWS * (VOB_MOE_PK / 8) + NT - 1) / NT;
+    const int tile = blockIdx.x;
+    const int e = tile_expert[tile];
+    if (e < 0) return;
+    extern __shared__ __align__(128) unsigned char moe_smem[];
+    __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(moe_smem);
+    __shared__ int pair_of[BM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, wc = warp & 3, wr = warp >> 2;
+    const int col0 = blockIdx.y * (DOWN ? 128 : 64);
+    // the rows this thread fetches, the same in every stage
+    const __nv_bfloat16* src[CHUNKS];
+    int dst_off[CHUNKS], feat[CHUNKS];
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+        const int el = tid + NT * i;
+        const int r = el / (VOB_MOE_PK / 8), c = (el % (VOB_MOE_PK / 8)) * 8;
+        src[i] = nullptr;
+        dst_off[i] = -1;
+        feat[i] = c;
+        if (r >= ROWS) continue;
+        dst_off[i] = r * VOB_MOE_PLD + c;
+        if (r < BM) {
+            const int p = sorted[tile * BM + r];
+            if (c == 0) pair_of[r] = p;
+            if (p >= 0) src[i] = a + (size_t)(p / a_div) * ld_a;
+        } else {
+            const int j = r - BM;
+            if (DOWN) {
+                if (col0 + j < N) src[i] = w + ((size_t)e * N + col0 + j) * K;
+            } else {
+                const int col = col0 + (j & 63);
+                if (col < N) src[i] = w + ((size_t)e * 2 * N + (j < 64 ? 0 : N) + col) * K;
+            }
+        }
+    }
+    auto fetch = [&](int stage, int k0) {
+        __nv_bfloat16* base = stages + (size_t)stage * ROWS * VOB_MOE_PLD;
+#pragma unroll
+        for (int i = 0; i < CHUNKS; ++i) {
+            if (dst_off[i] < 0) continue;
+            const int left = (K - k0 - feat[i]) * 2;
+            const int bytes = src[i] ? max(0, min(16, left)) : 0;
+            moe_cp16(base + dst_off[i], bytes > 0 ? (const void*)(src[i] + k0 + feat[i]) : (const void*)w, bytes);
+        }
+    };
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> c0[RF], c1[RF];
+#pragma unroll
+    for (int i = 0; i < RF; ++i) { wmma::fill_fragment(c0[i], 0.f); wmma::fill_fragment(c1[i], 0.f); }
+    const int nk = (K + VOB_MOE_PK - 1) / VOB_MOE_PK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < nk) fetch(s, s * VOB_MOE_PK);
+        moe_cp_commit();
+    }
+    for (int it = 0; it < nk; ++it) {
+        moe_cp_wait<STAGES - 2>();
+        __syncthreads();                                // stage `it` has arrived for everyone; stage `it - 1` is read by nobody
+        if (it + STAGES - 1 < nk) fetch((it + STAGES - 1) % STAGES, (it + STAGES - 1) * VOB_MOE_PK);
+        moe_cp_commit();
+        const __nv_bfloat16* As = stages + (size_t)(it % STAGES) * ROWS * VOB_MOE_PLD;
+        const __nv_bfloat16* Bs = As + BM * VOB_MOE_PLD;
+#pragma unroll
+        for (int kk = 0; kk < VOB_MOE_PK; kk += 16) {
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> b0, b1;
+            wmma::load_matrix_sync(b0, Bs + (wc * 16) * VOB_MOE_PLD + kk, VOB_MOE_PLD);
+            wmma::load_matrix_sync(b1, Bs + (64 + wc * 16) * VOB_MOE_PLD + kk, VOB_MOE_PLD);
+#pragma unroll
+            for (int i = 0; i < RF; ++i) {
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+                wmma::load_matrix_sync(fa, As + (wr * (BM / WR) + 16 * i) * VOB_MOE_PLD + kk, VOB_MOE_PLD);
+                wmma::mma_sync(c0[i], fa, b0, c0[i]);
+                wmma::mma_sync(c1[i], fa, b1, c1[i]);
+            }
+        }
+    }
+    moe_cp_wait<0>();
+    __syncthreads();                                    // the stages are free: each warp takes 2 KB of them for its results
+    float* Cs = reinterpret_cast<float*>(moe_smem) + warp * 512;
+#pragma unroll
+    for (int i = 0; i < RF; ++i) {
+        wmma::store_matrix_sync(Cs, c0[i], 16, wmma::mem_row_major);
+        wmma::store_matrix_sync(Cs + 256, c1[i], 16, wmma::mem_row_major);
+        __syncwarp();
+        for (int el = lane; el < 256; el += 32) {
+            const int r = el >> 4, c = el & 15;
+            const int p = pair_of[wr * (BM / WR) + 16 * i + r];
+            if (p < 0) continue;
+            if (DOWN) {
+                float* y = reinterpret_cast<float*>(out);
+                const float wgt = pair_w[p];
+                const int ca = col0 + wc * 16 + c, cb = ca + 64;
+                if (ca < N) y[(size_t)p * N + ca] = wgt * Cs[el];
+                if (cb < N) y[(size_t)p * N + cb] = wgt * Cs[256 + el];
+            } else {
+                const int col = col0 + wc * 16 + c;
+                if (col < N) {
+                    const float gr = __bfloat162float(__float2bfloat16_rn(Cs[el]));
+                    const float ur = __bfloat162float(__float2bfloat16_rn(Cs[256 + el]));
+                    reinterpret_cast<__nv_bfloat16*>(out)[(size_t)p * N + col] = __float2bfloat16_rn(moe_silu(gr) * ur);
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
+template <int BM, int STAGES, bool DOWN>
+static int moe_pipe_launch(dim3 grid, cudaStream_t stream, const __nv_bfloat16* a, long ld_a, int a_div, const __nv_bfloat16* w,
+                           const int* sorted, const int* tile_expert, const float* pair_w, int K, int N, void* out) {
+    const size_t smem = (size_t)STAGES * (BM + 128) * VOB_MOE_PLD * sizeof(__nv_bfloat16);
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t err = cudaFuncSetAttribute(moe_pipe_kernel<BM, STAGES, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+        raised = true;
+    }
+    return vob_launch(moe_pipe_kernel<BM, STAGES, DOWN>, grid, dim3(BM == 128 ? 256 : 128), smem, stream, a, ld_a, a_div, w, sorted,
+                      tile_expert, pair_w, K, N, out);
+}
+
+static inline bool moe_rows_by16(const void* p, long ld, int K) { return K % 8 == 0 && ld % 8 == 0 && (((uintptr_t)p) & 15) == 0; }
+
+// `tensor_cores` (bfloat16 only): the wmma forms, the pipelined one where the rows allow 16-byte copies. `tile_rows`: the rows
+// of a tile as the ordering made them (32; 128 only with the pipelined form). `max_tiles` = rows of `sorted` / tile_rows: the
+// grid covers them all and tiles behind the last one in use leave at once.
 VOB_EXPORT int vob_moe_gate_up(const void* x, int code, long ld_x, const void* w_gu, const int* sorted, const int* tile_expert,
-                               int max_tiles, int top, int width, int ff, void* h_out, int tensor_cores, cudaStream_t stream) {
+                               int max_tiles, int tile_rows, int top, int width, int ff, void* h_out, int tensor_cores, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     if (top <= 0 || width <= 0 || ff <= 0) return VOB_ERR_BAD_ARG;
+    if (tile_rows != VOB_MOE_BM && !(tile_rows == 128 && tensor_cores)) return VOB_ERR_BAD_ARG;
     if (tensor_cores) {
         if (code != VOB_BF16) return VOB_ERR_BAD_ARG;
         if ((ff + 63) / 64 > 65535) return VOB_ERR_UNSUPPORTED;
-        return vob_launch(moe_gate_up_tc_kernel, dim3(max_tiles, (ff + 63) / 64), dim3(128), 0, stream, (const __nv_bfloat16*)x, ld_x,
-                          (const __nv_bfloat16*)w_gu, sorted, tile_expert, top, width, ff, (__nv_bfloat16*)h_out);
+        const dim3 grid(max_tiles, (ff + 63) / 64);
+        const __nv_bfloat16 *xa = (const __nv_bfloat16*)x, *wa = (const __nv_bfloat16*)w_gu;
+        if (moe_rows_by16(x, ld_x, width) && moe_rows_by16(w_gu, width, width)) {
+            if (tile_rows == 128) return moe_pipe_launch<128, 3, false>(grid, stream, xa, ld_x, top, wa, sorted, tile_expert, nullptr, width, ff, h_out);
+            return moe_pipe_launch<32, 4, false>(grid, stream, xa, ld_x, top, wa, sorted, tile_expert, nullptr, width, ff, h_out);
+        }
+        if (tile_rows != VOB_MOE_BM) return VOB_ERR_UNSUPPORTED;
+        return vob_launch(moe_gate_up_tc_kernel, grid, dim3(128), 0, stream, xa, ld_x, wa, sorted, tile_expert, top, width, ff,
+                          (__nv_bfloat16*)h_out);
     }
     if ((ff + 31) / 32 > 65535) return VOB_ERR_UNSUPPORTED;
     VOB_DISPATCH_ELEM(code, return vob_launch(moe_gate_up_kernel<ElemT>, dim3(max_tiles, (ff + 31) / 32), dim3(256), 0, stream, (const ElemT*)x,
@@ -485,14 +687,22 @@ VOB_EXPORT int vob_moe_gate_up(const void* x, int code, long ld_x, const void* w
 }
 
 VOB_EXPORT int vob_moe_down(const void* h, int code, const void* w_down, const int* sorted, const int* tile_expert, const float* pair_w,
-                            int max_tiles, int width, int ff, float* y, int tensor_cores, cudaStream_t stream) {
+                            int max_tiles, int tile_rows, int width, int ff, float* y, int tensor_cores, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     if (width <= 0 || ff <= 0) return VOB_ERR_BAD_ARG;
+    if (tile_rows != VOB_MOE_BM && !(tile_rows == 128 && tensor_cores)) return VOB_ERR_BAD_ARG;
     if ((width + 63) / 64 > 65535) return VOB_ERR_UNSUPPORTED;
     if (tensor_cores) {
         if (code != VOB_BF16) return VOB_ERR_BAD_ARG;
-        return vob_launch(moe_down_tc_kernel, dim3(max_tiles, (width + 63) / 64), dim3(128), 0, stream, (const __nv_bfloat16*)h,
-                          (const __nv_bfloat16*)w_down, sorted, tile_expert, pair_w, width, ff, y);
+        const __nv_bfloat16 *ha = (const __nv_bfloat16*)h, *wa = (const __nv_bfloat16*)w_down;
+        if (moe_rows_by16(h, ff, ff) && moe_rows_by16(w_down, ff, ff)) {
+            const dim3 grid(max_tiles, (width + 127) / 128);
+            if (tile_rows == 128) return moe_pipe_launch<128, 3, true>(grid, stream, ha, ff, 1, wa, sorted, tile_expert, pair_w, ff, width, y);
+            return moe_pipe_launch<32, 4, true>(grid, stream, ha, ff, 1, wa, sorted, tile_expert, pair_w, ff, width, y);
+        }
+        if (tile_rows != VOB_MOE_BM) return VOB_ERR_UNSUPPORTED;
+        return vob_launch(moe_down_tc_kernel, dim3(max_tiles, (width + 63) / 64), dim3(128), 0, stream, ha, wa, sorted, tile_expert, pair_w,
+                          width, ff, y);
     }
     VOB_DISPATCH_ELEM(code, return vob_launch(moe_down_kernel<ElemT>, dim3(max_tiles, (width + 63) / 64), dim3(256), 0, stream, (const ElemT*)h,
                                               (const ElemT*)w_down, sorted, tile_expert, pair_w, width, ff, y));

@@ -1067,11 +1067,21 @@ def conv_state_update(proj: torch.Tensor, x_off: int, conv_state: torch.Tensor, 
 
 # ------------------------------------------------------------------------------------ mixture of experts
 MOE_TILE_ROWS = 32           # rows of a tile of (token, expert) pairs (VOB_MOE_BM of csrc/moe.cu)
+MOE_LARGE_TILE_ROWS = 128    # the pipelined tensor-core products also take tiles of this many
+MOE_LARGE_TILE_FROM = 64     # pairs an expert gets on average from which the large tiles are taken
 
 
-def moe_sorted_rows(pairs: int, experts: int) -> int:
+def moe_tile_rows(pairs: int, experts: int, width: int, ff: int, tensor_cores: bool) -> int:
+    """Rows of a tile for a step of `pairs` pairs: 128 where the tensor-core products can fetch their rows 16 bytes at a
+    time (width and ff multiples of 8) and the experts get enough pairs each to fill such tiles, else 32."""
+    if tensor_cores and width % 8 == 0 and ff % 8 == 0 and pairs >= MOE_LARGE_TILE_FROM * experts:
+        return MOE_LARGE_TILE_ROWS
+    return MOE_TILE_ROWS
+
+
+def moe_sorted_rows(pairs: int, experts: int, tile_rows: int = MOE_TILE_ROWS) -> int:
     """Rows the ordered list of `pairs` (token, expert) pairs takes: every expert's run is padded to whole tiles."""
-    return -(-pairs // MOE_TILE_ROWS) * MOE_TILE_ROWS + experts * MOE_TILE_ROWS
+    return -(-pairs // tile_rows) * tile_rows + experts * tile_rows
 
 
 @_timed
@@ -1103,36 +1113,42 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, positions: Optional[torch
 
 
 @_timed
-def moe_align(idx: torch.Tensor, experts: int, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, meta: torch.Tensor) -> None:
+def moe_align(idx: torch.Tensor, experts: int, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, meta: torch.Tensor,
+              tile_rows: int = MOE_TILE_ROWS) -> None:
     """The pairs idx [T, top] (expert of token t's k-th choice, -1: none) in order of their expert: sorted_pairs int32 [cap]
-    (pair number t * top + k, -1: padding; cap >= moe_sorted_rows(T * top, experts)), tile_expert int32 [cap / MOE_TILE_ROWS],
-    meta int32 [>= 1] (meta[0]: tiles in use)."""
+    (pair number t * top + k, -1: padding; cap >= moe_sorted_rows(T * top, experts, tile_rows)), tile_expert int32
+    [cap / tile_rows], meta int32 [>= 1] (meta[0]: tiles in use)."""
     op = "moe_align"
     _cuda(op, idx, sorted_pairs, tile_expert, meta)
     if idx.dtype != torch.int32 or idx.dim() != 2 or not idx.is_contiguous():
         raise ShapeError(op, f"idx must be contiguous int32 [T, top], got {idx.dtype} {list(idx.shape)}")
     P, cap = idx.numel(), sorted_pairs.numel()
-    if cap % MOE_TILE_ROWS or cap < moe_sorted_rows(P, experts):
-        raise ShapeError(op, f"sorted_pairs has {cap} rows, {moe_sorted_rows(P, experts)} (a multiple of {MOE_TILE_ROWS}) are needed")
+    if tile_rows not in (MOE_TILE_ROWS, MOE_LARGE_TILE_ROWS):
+        raise ShapeError(op, f"tiles have {MOE_TILE_ROWS} or {MOE_LARGE_TILE_ROWS} rows, not {tile_rows}")
+    if cap % tile_rows or cap < moe_sorted_rows(P, experts, tile_rows):
+        raise ShapeError(op, f"sorted_pairs has {cap} rows, {moe_sorted_rows(P, experts, tile_rows)} (a multiple of {tile_rows}) are needed")
     _int32_vec(sorted_pairs, cap, op, "sorted_pairs")
-    _int32_vec(tile_expert, cap // MOE_TILE_ROWS, op, "tile_expert")
+    _int32_vec(tile_expert, cap // tile_rows, op, "tile_expert")
     _int32_vec(meta, 1, op, "meta")
-    f = _fn("moe", "vob_moe_align", [_P, _I, _I, _P, _I, _P, _P, _P])
-    _check(f(_ptr(idx), P, int(experts), _ptr(sorted_pairs), cap, _ptr(tile_expert), _ptr(meta), _stream()), op)
+    f = _fn("moe", "vob_moe_align", [_P, _I, _I, _P, _I, _P, _P, _I, _P])
+    _check(f(_ptr(idx), P, int(experts), _ptr(sorted_pairs), cap, _ptr(tile_expert), _ptr(meta), int(tile_rows), _stream()), op)
 
 
-def _moe_tiles(op, sorted_pairs, tile_expert):
+def _moe_tiles(op, sorted_pairs, tile_expert, tile_rows, tensor_cores, width, ff):
     cap = sorted_pairs.numel()
     _int32_vec(sorted_pairs, cap, op, "sorted_pairs")
-    if cap % MOE_TILE_ROWS:
-        raise ShapeError(op, f"sorted_pairs must hold whole tiles of {MOE_TILE_ROWS}, got {cap}")
-    _int32_vec(tile_expert, cap // MOE_TILE_ROWS, op, "tile_expert")
-    return cap // MOE_TILE_ROWS
+    if tile_rows != MOE_TILE_ROWS and not (tile_rows == MOE_LARGE_TILE_ROWS and tensor_cores and width % 8 == 0 and ff % 8 == 0):
+        raise ShapeError(op, f"tiles of {tile_rows} rows: {MOE_TILE_ROWS}, or {MOE_LARGE_TILE_ROWS} with the tensor-core form and "
+                             f"width and ff multiples of 8")
+    if cap % tile_rows:
+        raise ShapeError(op, f"sorted_pairs must hold whole tiles of {tile_rows}, got {cap}")
+    _int32_vec(tile_expert, cap // tile_rows, op, "tile_expert")
+    return cap // tile_rows
 
 
 @_timed
 def moe_gate_up(x: torch.Tensor, w_gu: torch.Tensor, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, top: int,
-                h_out: torch.Tensor, tensor_cores: bool = False) -> None:
+                h_out: torch.Tensor, tensor_cores: bool = False, tile_rows: int = MOE_TILE_ROWS) -> None:
     """h_out[pair] = silu(W_gate[e] x[token]) * (W_up[e] x[token]) for every pair of the ordered list; w_gu [E, 2 ff, width]
     (an expert's gate rows, then its up rows) and h_out [T * top, ff] of x's type. `tensor_cores`: the bfloat16 tile form."""
     op = "moe_gate_up"
@@ -1146,15 +1162,17 @@ def moe_gate_up(x: torch.Tensor, w_gu: torch.Tensor, sorted_pairs: torch.Tensor,
         raise ShapeError(op, f"h_out must be contiguous {x.dtype} [{T * top}, {ff}], got {h_out.dtype} {list(h_out.shape)}")
     if tensor_cores and x.dtype != torch.bfloat16:
         raise ShapeError(op, "the tensor-core form takes bfloat16")
-    tiles = _moe_tiles(op, sorted_pairs, tile_expert)
-    f = _fn("moe", "vob_moe_gate_up", [_P, _I, _L, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P])
-    _check(f(_ptr(x), _code(x, op), x.stride(0), _ptr(w_gu), _ptr(sorted_pairs), _ptr(tile_expert), tiles, int(top), width, ff,
+    tiles = _moe_tiles(op, sorted_pairs, tile_expert, tile_rows, tensor_cores, width, ff)
+    if tile_rows != MOE_TILE_ROWS and (x.stride(0) % 8 or x.data_ptr() % 16):
+        raise ShapeError(op, f"tiles of {tile_rows} rows need rows of x that start on 16-byte boundaries")
+    f = _fn("moe", "vob_moe_gate_up", [_P, _I, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P])
+    _check(f(_ptr(x), _code(x, op), x.stride(0), _ptr(w_gu), _ptr(sorted_pairs), _ptr(tile_expert), tiles, int(tile_rows), int(top), width, ff,
              _ptr(h_out), 1 if tensor_cores else 0, _stream()), op)
 
 
 @_timed
 def moe_down(h: torch.Tensor, w_down: torch.Tensor, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, pair_w: torch.Tensor,
-             y: torch.Tensor, tensor_cores: bool = False) -> None:
+             y: torch.Tensor, tensor_cores: bool = False, tile_rows: int = MOE_TILE_ROWS) -> None:
     """y[pair] = pair_w[pair] * (W_down[e] h[pair]), float32 [T * top, width]; w_down [E, width, ff] of h's type; pair_w
     float32 [T, top]."""
     op = "moe_down"
@@ -1171,9 +1189,9 @@ def moe_down(h: torch.Tensor, w_down: torch.Tensor, sorted_pairs: torch.Tensor, 
         raise ShapeError(op, f"y must be contiguous float32 [{P}, {width}], got {y.dtype} {list(y.shape)}")
     if tensor_cores and h.dtype != torch.bfloat16:
         raise ShapeError(op, "the tensor-core form takes bfloat16")
-    tiles = _moe_tiles(op, sorted_pairs, tile_expert)
-    f = _fn("moe", "vob_moe_down", [_P, _I, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P])
-    _check(f(_ptr(h), _code(h, op), _ptr(w_down), _ptr(sorted_pairs), _ptr(tile_expert), _ptr(pair_w), tiles, width, ff, _ptr(y),
+    tiles = _moe_tiles(op, sorted_pairs, tile_expert, tile_rows, tensor_cores, width, ff)
+    f = _fn("moe", "vob_moe_down", [_P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P])
+    _check(f(_ptr(h), _code(h, op), _ptr(w_down), _ptr(sorted_pairs), _ptr(tile_expert), _ptr(pair_w), tiles, int(tile_rows), width, ff, _ptr(y),
              1 if tensor_cores else 0, _stream()), op)
 
 

@@ -8,7 +8,8 @@
 Per step: the election (one warp per token), the (token, expert) pairs put in order of their expert on the device
 (no count ever goes to the host, so the step can be recorded in a CUDA graph), one grouped product for gate and up
 with the gate in its epilogue, one for down with the weight in its epilogue, and the sum over a token's choices in
-their own order. bfloat16 engines run the products on the tensor cores (`tensor_cores`), float32 engines as plain
+their own order. A step in which the experts get many pairs each takes tiles of 128 pairs, else of 32 (the same sums
+either way). bfloat16 engines run the products on the tensor cores (`tensor_cores`), float32 engines as plain
 multiply-add chains over the features in order.
 """
 from __future__ import annotations
@@ -57,7 +58,7 @@ class RoutedExperts(FeedForward):
     def workspace_bytes(self, rows: int) -> int:
         es = 2 if self.dtype == torch.bfloat16 else 4
         P = rows * self.top
-        cap = kernels.moe_sorted_rows(P, self.E)
+        cap = max(kernels.moe_sorted_rows(P, self.E, r) for r in (kernels.MOE_TILE_ROWS, kernels.MOE_LARGE_TILE_ROWS))
         return (2 * aligned(P * 4) + aligned(cap * 4) + aligned(cap // kernels.MOE_TILE_ROWS * 4) + aligned(P * self.ff * es)
                 + aligned(P * self.hidden * 4) + aligned(rows * self.hidden * es))
 
@@ -69,13 +70,15 @@ class RoutedExperts(FeedForward):
         P = T * self.top
         idx, w = ctx.alloc((T, self.top), torch.int32), ctx.alloc((T, self.top), torch.float32)
         kernels.moe_route(x, self.w_router, ctx.positions, self.top, self.groups, self.keep, self.renorm, idx, w)
-        cap = kernels.moe_sorted_rows(P, self.E)
-        order, tile_expert = ctx.alloc((cap,), torch.int32), ctx.alloc((cap // kernels.MOE_TILE_ROWS,), torch.int32)
-        kernels.moe_align(idx, self.E, order, tile_expert, self.meta)
+        large = x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+        tile = kernels.moe_tile_rows(P, self.E, self.hidden, self.ff, self.tensor_cores and large)
+        cap = kernels.moe_sorted_rows(P, self.E, tile)
+        order, tile_expert = ctx.alloc((cap,), torch.int32), ctx.alloc((cap // tile,), torch.int32)
+        kernels.moe_align(idx, self.E, order, tile_expert, self.meta, tile)
         h = ctx.alloc((P, self.ff))
-        kernels.moe_gate_up(x, self.w_gu, order, tile_expert, self.top, h, self.tensor_cores)
+        kernels.moe_gate_up(x, self.w_gu, order, tile_expert, self.top, h, self.tensor_cores, tile)
         y = ctx.alloc((P, self.hidden), torch.float32)
-        kernels.moe_down(h, self.w_down, order, tile_expert, w, y, self.tensor_cores)
+        kernels.moe_down(h, self.w_down, order, tile_expert, w, y, self.tensor_cores, tile)
         out = out if out is not None else ctx.alloc((T, self.hidden))
         kernels.moe_combine(y, idx, out)
         return out
