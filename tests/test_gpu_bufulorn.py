@@ -178,7 +178,7 @@ def test_learned_positions_layer_norm_and_xielu():
     assert torch.equal(out[3], table[5].float()) and int(flag) == 0           # a padding row gets no position vector
     kernels.embed(table, toks, out, flag, 1.0, ptab, torch.tensor([8, 9, 3, 0], dtype=torch.int32, device=DEV))
     assert int(flag) == 1                                                      # a position beyond the table is reported
-    for h in (42, 64, 300):
+    for h in (42, 64, 300, 2052):           # single features, four at a time, and more than one turn of four a thread
         for dt in (torch.float32, torch.bfloat16):
             resid, delta = torch.randn(5, h, device=DEV) * 3, (torch.randn(5, h, device=DEV) * 2 + 0.7).to(dt)
             w, b = torch.randn(h, device=DEV), torch.randn(h, device=DEV)
@@ -200,14 +200,20 @@ def test_learned_positions_layer_norm_and_xielu():
     resid, delta = torch.zeros(1, 64, device=DEV), (1000.0 + torch.randn(1, 64, device=DEV) * 0.01)
     w, b = torch.ones(64, device=DEV), torch.zeros(64, device=DEV)
     kernels.layernorm_add(resid, delta, w, b, 1e-5)
-    assert max_rel_diff(resid, plain.layer_norm(delta.double(), w.double(), b.double(), 1e-5)) < 1e-3
+    # (float32 holds the mean of such a row to half a unit in its last place, 3e-5 here, a few thousandths of the deviations)
+    assert max_rel_diff(resid, plain.layer_norm(delta.double(), w.double(), b.double(), 1e-5)) < 1e-2
     p, q = torch.tensor(0.3), torch.tensor(-0.8)
     params = torch.tensor([float(plain.softplus(p)), 0.5 + float(plain.softplus(q))], device=DEV)
-    for cols in (30, 300):
-        z = torch.randn(4, cols + 3, device=DEV) * 3
-        act = torch.empty(4, cols, device=DEV)
-        kernels.activation(z[:, :cols], act, "xielu", params)
-        assert max_rel_diff(act, plain.xielu(z[:, :cols].double(), p.double(), q.double())) < 1e-6
+    for cols, spare in ((30, 3), (300, 3), (300, 4), (2056, 8), (2056, 0)):    # rows read feature by feature, and 16 bytes at a time
+        for dt in (torch.float32, torch.bfloat16):
+            z = (torch.randn(4, cols + spare, device=DEV) * 3).to(dt)
+            act = torch.empty(4, cols, dtype=dt, device=DEV)
+            kernels.activation(z[:, :cols], act, "xielu", params)
+            want = plain.xielu(z[:, :cols].double(), p.double(), q.double())
+            assert max_rel_diff(act, want) < (1e-6 if dt == torch.float32 else 5e-3)
+            if spare == 0:
+                kernels.activation(z, z, "xielu", params)                     # in place
+                assert torch.equal(z, act)
 
 
 # ------------------------------------------------------------------------------------ attention kernels

@@ -626,39 +626,98 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
     return t;
 }
 
-template <typename TD, typename TO>
+template <typename T> __device__ __forceinline__ void ld4_f(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void ld4_f<float>(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+template <> __device__ __forceinline__ void ld4_f<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 a = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&a.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
+    v[0] = __bfloat162float(lo.x); v[1] = __bfloat162float(lo.y); v[2] = __bfloat162float(hi.x); v[3] = __bfloat162float(hi.y);
+}
+template <typename T> __device__ __forceinline__ void st4_f(T* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void st4_f<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void st4_f<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 a;
+    a.x = *reinterpret_cast<const unsigned*>(&lo);
+    a.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = a;
+}
+
+// BY4: the row's length is a multiple of 4 and every row starts where four features can be read at once; a thread
+// then takes four neighbouring features a turn (its partial sums run over them in order).
+template <typename TD, typename TO, bool BY4>
 __global__ void __launch_bounds__(256)
 layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
                  const float* __restrict__ bias, const int* __restrict__ rows, TO* __restrict__ out, int h, float eps) {
     pdl_launch_dependents();
     pdl_wait(5);
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float red[8];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* x = resid + (size_t)src * h;
     const TD* d = delta ? delta + (size_t)r * h : nullptr;
     float s = 0.f;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-        const float v = d ? ld_f(d + i) : x[i];
-        row[i] = v;
-        s += v;
+    if (BY4) {
+        for (int i = threadIdx.x * 4; i < h; i += 1024) {
+            float v[4];
+            if (d) ld4_f<TD>(d + i, v); else ld4_f<float>(x + i, v);
+            st4_f<float>(row + i, v);
+            s += v[0]; s += v[1]; s += v[2]; s += v[3];
+        }
+    } else {
+        for (int i = threadIdx.x; i < h; i += blockDim.x) {
+            const float v = d ? ld_f(d + i) : x[i];
+            row[i] = v;
+            s += v;
+        }
     }
     const float mean = block_sum_256(s, red) / (float)h;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-        const float c = row[i] - mean;
-        ss = fmaf(c, c, ss);
+    if (BY4) {
+        for (int i = threadIdx.x * 4; i < h; i += 1024) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float c = row[i + k] - mean;
+                ss = fmaf(c, c, ss);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < h; i += blockDim.x) {
+            const float c = row[i] - mean;
+            ss = fmaf(c, c, ss);
+        }
     }
     const float inv = 1.0f / sqrtf(block_sum_256(ss, red) / (float)h + eps);
     TO* o = out ? out + (size_t)r * h : nullptr;
-    for (int i = threadIdx.x; i < h; i += blockDim.x) {
-        float y = (row[i] - mean) * inv * weight[i] + bias[i];
-        if (d) {
-            y += x[i];
-            x[i] = y;
+    if (BY4) {
+        for (int i = threadIdx.x * 4; i < h; i += 1024) {
+            float y[4], w4[4], b4[4], x4[4];
+            ld4_f<float>(weight + i, w4);
+            ld4_f<float>(bias + i, b4);
+            if (d) ld4_f<float>(x + i, x4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                y[k] = (row[i + k] - mean) * inv * w4[k] + b4[k];
+                if (d) y[k] += x4[k];
+            }
+            if (d) st4_f<float>(x + i, y);
+            if (o) st4_f<TO>(o + i, y);
         }
-        if (o) st_f(o + i, y);
+    } else {
+        for (int i = threadIdx.x; i < h; i += blockDim.x) {
+            float y = (row[i] - mean) * inv * weight[i] + bias[i];
+            if (d) {
+                y += x[i];
+                x[i] = y;
+            }
+            if (o) st_f(o + i, y);
+        }
     }
 }
 
@@ -670,7 +729,13 @@ VOB_EXPORT int vob_layernorm(float* resid, const void* delta, int delta_code, co
     if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
     if (!delta) delta_code = VOB_F32;
     if (!out) out_code = VOB_F32;
-#define VOB_LN(TD_, TO_) return vob_launch(layernorm_kernel<TD_, TO_>, dim3(R), dim3(256), smem, stream, resid, (const TD_*)delta, weight, bias, rows, (TO_*)out, h, eps)
+    const bool by4 = h % 4 == 0 && ((((uintptr_t)resid) | ((uintptr_t)weight) | ((uintptr_t)bias)) & 15) == 0 && (((uintptr_t)delta) & 15) == 0 &&
+                     (((uintptr_t)out) & 15) == 0;
+#define VOB_LN(TD_, TO_)                                                                                                             \
+    return by4 ? vob_launch(layernorm_kernel<TD_, TO_, true>, dim3(R), dim3(256), smem, stream, resid, (const TD_*)delta, weight, bias, rows, \
+                            (TO_*)out, h, eps)                                                                                       \
+               : vob_launch(layernorm_kernel<TD_, TO_, false>, dim3(R), dim3(256), smem, stream, resid, (const TD_*)delta, weight, bias, rows, \
+                            (TO_*)out, h, eps)
     if (delta_code == VOB_F32 && out_code == VOB_F32) VOB_LN(float, float);
     if (delta_code == VOB_BF16 && out_code == VOB_BF16) VOB_LN(__nv_bfloat16, __nv_bfloat16);
     if (delta_code == VOB_F32 && out_code == VOB_BF16) VOB_LN(float, __nv_bfloat16);
@@ -705,6 +770,10 @@ VOB_EXPORT int vob_cast_rows(const float* in, void* out, int out_code, long long
 //       z > 0:  ap z^2 + z / 2;      z <= 0:  an (exp(z) - 1 - z) + z / 2
 // in [T, I] with a row stride, out [T, I] contiguous (may be `in` itself when that is contiguous).
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float xielu_f(float z, float ap, float an) {
+    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 act_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I, int act, const float* __restrict__ params) {
@@ -715,14 +784,44 @@ act_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, i
     if (j >= I) return;
     const float ap = params[0], an = params[1];
     const float z = ld_f(in + (size_t)t * in_stride + j);
-    const float y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
-    st_f(out + (size_t)t * I + j, y);
+    st_f(out + (size_t)t * I + j, xielu_f(z, ap, an));
+}
+
+// Rows whose length and addresses allow 16-byte accesses: a thread takes 16 bytes of a row a turn.
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I, int act, const float* __restrict__ params) {
+    pdl_launch_dependents();
+    pdl_wait(7);
+    constexpr int PER = 16 / sizeof(T);
+    const int t = blockIdx.x;
+    const int j = (blockIdx.y * 256 + threadIdx.x) * PER;
+    if (j >= I) return;
+    const float ap = params[0], an = params[1];
+    const T* src = in + (size_t)t * in_stride + j;
+    T* dst = out + (size_t)t * I + j;
+#pragma unroll
+    for (int k = 0; k < PER; k += 4) {
+        float v[4];
+        ld4_f<T>(src + k, v);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) v[m] = xielu_f(v[m], ap, an);
+        st4_f<T>(dst + k, v);
+    }
 }
 
 VOB_EXPORT int vob_act(const void* in, long long in_stride, void* out, int code, int T, int I, int act, const float* params,
                        cudaStream_t stream) {
     if (T <= 0) return 0;
     if (I <= 0 || act != 0 || !params) return VOB_ERR_BAD_ARG;
+    const int per = code == VOB_BF16 ? 8 : 4;
+    if (I % per == 0 && in_stride % per == 0 && ((((uintptr_t)in) | ((uintptr_t)out)) & 15) == 0) {
+        const int by = (I / per + 255) / 256;
+        if (by > 65535) return VOB_ERR_UNSUPPORTED;
+        VOB_DISPATCH_ELEM(code, return vob_launch(act_vec_kernel<ElemT>, dim3(T, by), dim3(256), 0, stream, (const ElemT*)in, in_stride,
+                                                  (ElemT*)out, I, act, params));
+        return 0;
+    }
     if ((I + 255) / 256 > 65535) return VOB_ERR_UNSUPPORTED;
     VOB_DISPATCH_ELEM(code, return vob_launch(act_kernel<ElemT>, dim3(T, (I + 255) / 256), dim3(256), 0, stream, (const ElemT*)in, in_stride,
                                               (ElemT*)out, I, act, params));
