@@ -697,17 +697,19 @@ layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const 
     TO* o = out ? out + (size_t)r * h : nullptr;
     if (BY4) {
         for (int i = threadIdx.x * 4; i < h; i += 1024) {
-            float y[4], w4[4], b4[4], x4[4];
-            ld4_f<float>(weight + i, w4);
-            ld4_f<float>(bias + i, b4);
-            if (d) ld4_f<float>(x + i, x4);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                y[k] = (row[i + k] - mean) * inv * w4[k] + b4[k];
-                if (d) y[k] += x4[k];
+            const float4 w4 = *reinterpret_cast<const float4*>(weight + i), b4 = *reinterpret_cast<const float4*>(bias + i);
+            const float4 r4 = *reinterpret_cast<const float4*>(row + i);
+            float4 y = make_float4((r4.x - mean) * inv * w4.x + b4.x, (r4.y - mean) * inv * w4.y + b4.y,
+                                   (r4.z - mean) * inv * w4.z + b4.z, (r4.w - mean) * inv * w4.w + b4.w);
+            if (d) {
+                const float4 x4 = *reinterpret_cast<const float4*>(x + i);
+                y.x += x4.x; y.y += x4.y; y.z += x4.z; y.w += x4.w;
+                *reinterpret_cast<float4*>(x + i) = y;
             }
-            if (d) st4_f<float>(x + i, y);
-            if (o) st4_f<TO>(o + i, y);
+            if (o) {
+                const float yv[4] = {y.x, y.y, y.z, y.w};
+                st4_f<TO>(o + i, yv);
+            }
         }
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
