@@ -91,7 +91,10 @@ class CachePools:
         # (a mixer that names several tensors gets a tuple of them)
         self.state: Dict[int, object] = {}
         for idx, call in enumerate(spec.schedule):
-            ss = spec.blocks[call.layer].mixer.state_spec()
+            # a block may keep state of its own beside its mixer's (the last inputs of a convolution in front of its
+            # sub-layers, say): it then answers for both
+            block = spec.blocks[call.layer]
+            ss = block.state_spec() if hasattr(block, "state_spec") else block.mixer.state_spec()
             if ss is None:
                 continue
             made = tuple(torch.zeros((max_seqs,) + tuple(x.shape), dtype=x.dtype, device=device)

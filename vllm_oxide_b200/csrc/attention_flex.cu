@@ -10,6 +10,8 @@
 //   vob_flex_attention per (row, head a), the row at position p of its request, g = a / (H / G):
 //       s_j = (q'_a . K[j, g]) * scale          for keys j in [first, p], first = max(0, p + 1 - window), and with
 //                                                `chunk` not before p - p % chunk (the query's own block of positions)
+//       with `pool` (and a window): every block of `pool` positions that ends at or before p - window is one more key and
+//                                                value, the means of the block's keys and values, in the same softmax
 //       s_j <- cap * tanh(s_j / cap)  (cap > 0);   s_j <- s_j - r1_a * ln(1 + r2_a * (p - j))  (r1, r2 given)
 //       den = sum_j exp(s_j) (+ exp(sink_a): a key with no value, counted once)
 //       out_a = sum_j exp(s_j) V[j, g] / den    (* sigmoid(gate) * out_scale)
@@ -28,6 +30,8 @@ VOB_PDL_SWITCH(attention_flex)
 //          float(pos) * inv_freq[i]; then (unit_rms) the head is divided by sqrt(mean(x^2) + eps) and, where a
 //          weight of D entries is given (`q_norm_w`, `k_norm_w`, shared by the heads), multiplied by it;
 //          q is also multiplied by 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) (temp_every > 0).
+//          With `q_pre_w` [H * D] / `k_pre_w` [G * D]: BEFORE the rotation the whole projection (all heads at once) is
+//          divided by its root mean square, sqrt(mean over all its features of x^2 + eps), and multiplied by that weight.
 //   v:     v_mode 1: the values are also left in `v_first` [T, G * DV] for later layers of this step;
 //          v_mode 2: v <- (1 - lambda) v + lambda v_first, lambda = *vmix.
 // Rows with a negative position (padding) are left alone; a negative slot skips the cache write. Without a cache
@@ -39,7 +43,7 @@ __global__ void __launch_bounds__(256, 4)
 flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int v_off, const int* __restrict__ positions,
                  const int* __restrict__ slots, const float* __restrict__ inv_freq, int rot, int unit_rms, float eps,
                  float temp_coef, int temp_every, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
-                 const float* __restrict__ vmix, T* __restrict__ v_first, int v_mode, T* __restrict__ q_out, long ld_q, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D, int DV,
+                 const float* __restrict__ q_pre_w, const float* __restrict__ k_pre_w, const float* __restrict__ vmix, T* __restrict__ v_first, int v_mode, T* __restrict__ q_out, long ld_q, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int D, int DV,
                  int page_size) {
     pdl_launch_dependents();
     pdl_wait(61);
@@ -61,6 +65,26 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
                 const int f = lane + 32 * i;
                 x[i] = f < D ? ld_f(src + f) : 0.f;
                 y[i] = f < rot ? ld_f(src + (f < half ? f + half : f - half)) : 0.f;
+            }
+            const float* pre_w = is_q ? q_pre_w : k_pre_w;
+            if (pre_w) {
+                // a norm over the WHOLE projection (all heads of q, or of k, at once) with a weight per feature, before the
+                // rotation: every warp sums the projection's squares for itself (the same sum in the same order)
+                const int n = (is_q ? H : G) * D;
+                const T* base = row + (is_q ? q_off : k_off);
+                float sq = 0.f;
+                for (int f = lane; f < n; f += 32) {
+                    const float v = ld_f(base + f);
+                    sq = fmaf(v, v, sq);
+                }
+                const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)n + eps);
+                const float* hw = pre_w + (size_t)head * D;
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int f = lane + 32 * i;
+                    if (f < D) x[i] *= inv * hw[f];
+                    if (f < rot) y[i] *= inv * hw[f < half ? f + half : f - half];
+                }
             }
             if (pos < 0) return;
             const float fpos = (float)pos;
@@ -110,7 +134,8 @@ flex_prep_kernel(const T* __restrict__ proj, long ld, int q_off, int k_off, int 
 
 VOB_EXPORT int vob_flex_prep(const void* proj, int code, long ld, int q_off, int k_off, int v_off, const int* positions,
                              const int* slots, const float* inv_freq, int rot, int unit_rms, float eps, float temp_coef,
-                             int temp_every, const float* q_norm_w, const float* k_norm_w, const float* vmix, void* v_first,
+                             int temp_every, const float* q_norm_w, const float* k_norm_w, const float* q_pre_w, const float* k_pre_w,
+                             const float* vmix, void* v_first,
                              int v_mode, void* q_out, long ld_q, void* kcache,
                              void* vcache, int T, int H, int G, int D, int DV, int page_size, cudaStream_t stream) {
     if (T <= 0) return 0;
@@ -123,7 +148,7 @@ VOB_EXPORT int vob_flex_prep(const void* proj, int code, long ld, int q_off, int
 #define VOB_PREP(NI_)                                                                                                                  \
     VOB_DISPATCH_ELEM(code, return vob_launch(flex_prep_kernel<ElemT, NI_>, dim3(T, (H + 2 * G + 7) / 8), dim3(256), 0, stream,              \
                                               (const ElemT*)proj, ld, q_off, k_off, v_off, positions, slots, inv_freq, rot, unit_rms, eps,  \
-                                              temp_coef, temp_every, q_norm_w, k_norm_w, vmix, (ElemT*)v_first, v_mode, (ElemT*)q_out,  \
+                                              temp_coef, temp_every, q_norm_w, k_norm_w, q_pre_w, k_pre_w, vmix, (ElemT*)v_first, v_mode, (ElemT*)q_out,  \
                                               ld_q, (ElemT*)kcache,                                                                      \
                                               (ElemT*)vcache, H, G, D, DV, page_size))
     if (D <= 32) VOB_PREP(1);
@@ -173,7 +198,7 @@ flex_attention_warp_kernel(const T* __restrict__ q, long q_stride, T* __restrict
                            int max_pages, const int* __restrict__ row_seq, const int* __restrict__ positions, int T_rows, int H,
                            int G, int D, int DV, int page_size, int window, float scale, const float* __restrict__ sink,
                            const T* __restrict__ gate, long gate_stride, float out_scale, int chunk, float softcap,
-                           const float* __restrict__ dist_r1, const float* __restrict__ dist_r2) {
+                           const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, int pool) {
     pdl_launch_dependents();
     pdl_wait(62);
     extern __shared__ float qs_all[];
@@ -205,6 +230,57 @@ flex_attention_warp_kernel(const T* __restrict__ q, long q_stride, T* __restrict
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
+    if (pool > 0 && window > 0) {
+        // Behind the window every block of `pool` positions that lies wholly before it counts as ONE key and value, the
+        // means of its keys and of its values: q . mean(k) = mean(q . k), and its weight goes to each value divided by pool.
+        // Block b is seen when b * pool + pool - 1 <= pos - window. A lane scores one block; no distance bias here.
+        const int nblk = pos - window + 1 >= pool ? (pos - window + 1) / pool : 0;
+        const float inv_pool = 1.0f / (float)pool;
+        for (int b0 = 0; b0 < nblk; b0 += 32) {
+            const int b = b0 + lane;
+            const bool valid = b < nblk;
+            float s = -INFINITY;
+            if (valid) {
+                float dot = 0.f;
+                for (int jj = 0; jj < pool; ++jj) {
+                    const int j = b * pool + jj;
+                    const T* kp = kcache + (size_t)((bt[j / page_size] * G + g) * page_size + (j % page_size)) * D;
+                    if (vec) {
+                        for (int d = 0; d < D; d += VN) {
+                            float kv[VN];
+                            Vec16<T>::load(kp + d, kv);
+#pragma unroll
+                            for (int i = 0; i < VN; ++i) dot = fmaf(qs[d + i], kv[i], dot);
+                        }
+                    } else {
+                        for (int d = 0; d < D; ++d) dot = fmaf(qs[d], ld_f(kp + d), dot);
+                    }
+                }
+                s = dot * inv_pool * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            }
+            const float m_new = fmaxf(m, warp_max(s));
+            const float p = valid ? expf(s - m_new) : 0.f;
+            const float alpha = expf(m - m_new);
+            l = l * alpha + warp_sum(p);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+            m = m_new;
+            const int nb = min(32, nblk - b0);
+            for (int jb = 0; jb < nb; ++jb) {
+                const float pj = __shfl_sync(0xffffffffu, p, jb) * inv_pool;
+                for (int jj = 0; jj < pool; ++jj) {
+                    const int j = (b0 + jb) * pool + jj;
+                    const T* vp = vcache + (size_t)((bt[j / page_size] * G + g) * page_size + (j % page_size)) * DV;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int d = lane + 32 * i;
+                        if (d < DV) acc[i] = fmaf(pj, ld_f(vp + d), acc[i]);
+                    }
+                }
+            }
+        }
+    }
     for (int c0 = first; c0 <= pos; c0 += 32) {
         const int j = c0 + lane;
         const bool valid = j <= pos;
@@ -273,11 +349,12 @@ VOB_EXPORT int vob_flex_attention(const void* q, long q_stride, void* out, long 
                                   int code, const int* block_tables, int max_pages, const int* row_seq, const int* positions,
                                   int T_rows, int H, int G, int D, int DV, int page_size, int window, float scale,
                                   const float* sink, const void* gate, long gate_stride, float out_scale, int chunk, float softcap,
-                                  const float* dist_r1, const float* dist_r2, cudaStream_t stream) {
+                                  const float* dist_r1, const float* dist_r2, int pool, cudaStream_t stream) {
     if (T_rows <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G != 0 || page_size <= 0 || max_pages <= 0 || D <= 0 || DV <= 0) return VOB_ERR_BAD_ARG;
     if (D > 256 || DV > 256) return VOB_ERR_UNSUPPORTED;
-    if (chunk < 0 || softcap < 0.f || (dist_r1 != nullptr) != (dist_r2 != nullptr)) return VOB_ERR_BAD_ARG;
+    if (chunk < 0 || softcap < 0.f || (dist_r1 != nullptr) != (dist_r2 != nullptr) || pool < 0 || (pool > 0 && (window <= 0 || chunk > 0)))
+        return VOB_ERR_BAD_ARG;
     const long long warps = (long long)T_rows * H;
     const long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) return VOB_ERR_UNSUPPORTED;
@@ -286,6 +363,6 @@ VOB_EXPORT int vob_flex_attention(const void* q, long q_stride, void* out, long 
                                               (const ElemT*)q, q_stride, (ElemT*)out, out_stride, (const ElemT*)kcache,
                                               (const ElemT*)vcache, block_tables, max_pages, row_seq, positions, T_rows, H, G, D, DV,
                                               page_size, window, scale, sink, (const ElemT*)gate, gate_stride, out_scale, chunk, softcap,
-                                              dist_r1, dist_r2));
+                                              dist_r1, dist_r2, pool));
     return 0;
 }

@@ -607,7 +607,58 @@ VOB_EXPORT int vob_glu(const void* in, long long in_stride, void* out, int code,
 }
 
 // ---------------------------------------------------------------------------------------------
-// Layer norm with weight and bias, LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * w + b, in two arrangements:
+// The clamped gate of a feed-forward: g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(1.702 g) * (u + 1).
+// in [T, >= 2 I] (gate columns, then up columns, rows `in_stride` apart), out [T, I]. Grid (T, ceil(I / 256)).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_clamped_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, int I, float limit) {
+    pdl_launch_dependents();
+    pdl_wait(5);
+    const int j = blockIdx.y * 256 + threadIdx.x;
+    if (j >= I) return;
+    const T* r = in + (size_t)blockIdx.x * in_stride;
+    const float g = fminf(ld_f(r + j), limit), u = fminf(fmaxf(ld_f(r + I + j), -limit), limit);
+    st_f(out + (size_t)blockIdx.x * I + j, g / (1.0f + expf(-1.702f * g)) * (u + 1.0f));
+}
+
+VOB_EXPORT int vob_glu_clamped(const void* in, long long in_stride, void* out, int code, int T, int I, float limit, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (I <= 0 || !(limit > 0.f) || (I + 255) / 256 > 65535) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(code, return vob_launch(glu_clamped_kernel<ElemT>, dim3(T, (I + 255) / 256), dim3(256), 0, stream, (const ElemT*)in,
+                                              in_stride, (ElemT*)out, I, limit));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// A stream that is a learned weighted sum over depth. `stack` float32 [T, slots, h] keeps the embedding's output (slot 0)
+// and every layer's result so far; `x` float32 [T, h] holds the newest result:
+//   stack[t, n] = x[t];   x[t] = sum over j = 0 .. n of w[j] * stack[t, j]      (j in order, float32)
+// With `first` the kernel only files x as slot 0 (n = 0, x unchanged). Launch: grid (T, ceil(h / 256)).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+depth_average_kernel(float* __restrict__ stack, float* __restrict__ x, const float* __restrict__ w, int slots, int h, int n, int first) {
+    pdl_launch_dependents();
+    pdl_wait(7);
+    const int t = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
+    if (c >= h) return;
+    float* base = stack + (size_t)t * slots * h + c;
+    const float cur = x[(size_t)t * h + c];
+    base[(size_t)n * h] = cur;
+    if (first) return;
+    float acc = 0.f;
+    for (int j = 0; j < n; ++j) acc = fmaf(w[j], base[(size_t)j * h], acc);
+    x[(size_t)t * h + c] = fmaf(w[n], cur, acc);
+}
+
+VOB_EXPORT int vob_depth_average(float* stack, float* x, const float* w, int T, int slots, int h, int n, int first, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (h <= 0 || slots <= 0 || n < 0 || n >= slots || (!first && !w) || (h + 255) / 256 > 65535) return VOB_ERR_BAD_ARG;
+    return vob_launch(depth_average_kernel, dim3(T, (h + 255) / 256), dim3(256), 0, stream, stack, x, w, slots, h, n, first);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layer norm with weight and bias (`bias` null: none), LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * w + b, in two arrangements:
 //   delta given:  y = LN(delta[r]);  resid[r] += y  (the residual takes the NORMED result of a sub-layer, float32);
 //                 copy[r] = resid[r] in the activations' type, if `copy` is given (what the next sub-layer reads)
 //   delta null:   out[r] = LN(resid[rows ? rows[r] : r])   (the model's last norm on the wanted rows)
@@ -697,7 +748,8 @@ layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const 
     TO* o = out ? out + (size_t)r * h : nullptr;
     if (BY4) {
         for (int i = threadIdx.x * 4; i < h; i += 1024) {
-            const float4 w4 = *reinterpret_cast<const float4*>(weight + i), b4 = *reinterpret_cast<const float4*>(bias + i);
+            const float4 w4 = *reinterpret_cast<const float4*>(weight + i);
+            const float4 b4 = bias ? *reinterpret_cast<const float4*>(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             const float4 r4 = *reinterpret_cast<const float4*>(row + i);
             float4 y = make_float4((r4.x - mean) * inv * w4.x + b4.x, (r4.y - mean) * inv * w4.y + b4.y,
                                    (r4.z - mean) * inv * w4.z + b4.z, (r4.w - mean) * inv * w4.w + b4.w);
@@ -713,7 +765,7 @@ layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const 
         }
     } else {
         for (int i = threadIdx.x; i < h; i += blockDim.x) {
-            float y = (row[i] - mean) * inv * weight[i] + bias[i];
+            float y = (row[i] - mean) * inv * weight[i] + (bias ? bias[i] : 0.f);
             if (d) {
                 y += x[i];
                 x[i] = y;
@@ -726,7 +778,7 @@ layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const 
 VOB_EXPORT int vob_layernorm(float* resid, const void* delta, int delta_code, const float* weight, const float* bias,
                              const int* rows, void* out, int out_code, int R, int h, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
-    if (h <= 0 || !weight || !bias || (delta && rows) || (!delta && !out)) return VOB_ERR_BAD_ARG;
+    if (h <= 0 || !weight || (delta && rows) || (!delta && !out)) return VOB_ERR_BAD_ARG;
     const size_t smem = (size_t)h * sizeof(float);
     if (smem > 48 * 1024) return VOB_ERR_UNSUPPORTED;
     if (!delta) delta_code = VOB_F32;

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(256, 1)
 latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, const float* __restrict__ q_rot,
                      const TC* __restrict__ lat, const TC* __restrict__ kr, const int* __restrict__ block_tables, int max_pages,
                      const int* __restrict__ row_seq, const int* __restrict__ positions, int page_size, int H, int L, int R,
-                     float scale, int KT, TO* __restrict__ out, long o_ts, long o_hs, int splits, float* __restrict__ part) {
+                     float scale, int KT, TO* __restrict__ out, long o_ts, long o_hs, int splits, float* __restrict__ part, int window) {
     pdl_launch_dependents();
     pdl_wait(46);
     extern __shared__ float tile[];                 // [KT][L + R]
@@ -127,9 +127,11 @@ latent_attend_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, cons
         qr[i] = (head && c < R) ? q_rot[((size_t)t * H + h) * R + c] : 0.f;
     }
     float m = -INFINITY, l = 0.f;
-    const int share = ((pos + splits) / splits + KT - 1) / KT * KT;      // keys per block, whole tiles
-    const int nkeys = min(pos + 1, (int)(blockIdx.z + 1) * share);
-    for (int k0 = blockIdx.z * share; k0 < nkeys; k0 += KT) {
+    // the keys a row sees: all up to its own, or with a window only the last `window` of them
+    const int first = window > 0 ? max(0, pos + 1 - window) : 0;
+    const int share = ((pos - first + splits) / splits + KT - 1) / KT * KT;      // keys per block, whole tiles
+    const int nkeys = min(pos + 1, first + (int)(blockIdx.z + 1) * share);
+    for (int k0 = first + blockIdx.z * share; k0 < nkeys; k0 += KT) {
         const int n = min(KT, nkeys - k0);
         __syncthreads();
         // a warp copies whole keys (one page lookup per key, then consecutive elements)
@@ -240,8 +242,9 @@ latent_merge_kernel(const float* __restrict__ part, const int* __restrict__ posi
 VOB_EXPORT int vob_latent_attend(const float* q_lat, long q_ts, long q_hs, const float* q_rot, const void* lat, const void* kr,
                                  int cache_code, const int* block_tables, int max_pages, const int* row_seq, const int* positions,
                                  int page_size, int T, int H, int L, int R, float scale, void* out, int out_code, long o_ts, long o_hs,
-                                 int splits, float* part, cudaStream_t stream) {
+                                 int splits, float* part, int window, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (window < 0) return VOB_ERR_BAD_ARG;
     if (H <= 0 || L <= 0 || R <= 0 || page_size <= 0 || max_pages <= 0 || cache_code != out_code) return VOB_ERR_BAD_ARG;
     if (splits < 1 || splits > 65535 || (splits > 1 && !part) || H > 65535) return VOB_ERR_BAD_ARG;
     if (L > 1024 || R > 128) return VOB_ERR_UNSUPPORTED;
@@ -256,7 +259,7 @@ VOB_EXPORT int vob_latent_attend(const float* q_lat, long q_ts, long q_hs, const
 #define VOB_LA(N, TC)                                                                                                          \
     status = vob_launch(latent_attend_kernel<N, TC, TC>, grid, block, smem, stream, q_lat, q_ts, q_hs, q_rot, (const TC*)lat, \
                         (const TC*)kr, block_tables, max_pages, row_seq, positions, page_size, H, L, R, scale, KT, (TC*)out, o_ts, o_hs, \
-                        splits, part)
+                        splits, part, window)
 #define VOB_LA_N(TC)                       \
     do {                                   \
         if (nl <= 4) { VOB_LA(4, TC); }        \
@@ -312,7 +315,7 @@ __global__ void __launch_bounds__(256, 1)
 latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, const float* __restrict__ q_rot,
                         const __nv_bfloat16* __restrict__ lat, const __nv_bfloat16* __restrict__ kr, const int* __restrict__ block_tables,
                         int max_pages, const int* __restrict__ seq_starts, const int* __restrict__ positions, int page_size, int H, int L,
-                        int R, float scale, __nv_bfloat16* __restrict__ out, long o_ts, long o_hs, int WPH, int colsw) {
+                        int R, float scale, __nv_bfloat16* __restrict__ out, long o_ts, long o_hs, int WPH, int colsw, int window) {
     constexpr int BN = VOB_LTC_BN;
     pdl_launch_dependents();
     pdl_wait(48);
@@ -336,6 +339,11 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
         Q[i * DP + c] = __float2bfloat16_rn(v);
     }
     const int pos0 = positions[r0], pos_hi = pos0 + nrows - 1;
+    // with a window a row sees only its last `window` keys: the tile's first row bounds the keys from below (pages before
+    // that may have been given back and are never addressed), and the walk starts at the tile of BN keys that holds it, so
+    // that a row's keys fall into the same tiles however the prompt was cut
+    const int key_lo = window > 0 ? max(0, pos0 + 1 - window) : 0;
+    const int k_start = key_lo / BN * BN;
     const int* table = block_tables + (size_t)s * max_pages;
     // this warp's latent columns, in groups of 16
     const int col0 = wsub * colsw;
@@ -360,7 +368,7 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
             if (x < tile_pieces) {
                 const int kk = x / pieces, c = x - kk * pieces;
                 const int key = k0 + kk;
-                if (key <= pos_hi) {
+                if (key <= pos_hi && key >= key_lo) {
                     const size_t slot = (size_t)table[key / page_size] * page_size + key % page_size;
                     val = c < lat_chunks ? reinterpret_cast<const uint4*>(lat + slot * L)[c]
                                          : reinterpret_cast<const uint4*>(kr + slot * R)[c - lat_chunks];
@@ -369,8 +377,8 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
             nxt[i] = val;
         }
     };
-    fetch(0);
-    for (int k0 = 0; k0 <= pos_hi; k0 += BN) {
+    fetch(k_start);
+    for (int k0 = k_start; k0 <= pos_hi; k0 += BN) {
         __syncthreads();
 #pragma unroll
         for (int i = 0; i < VOB_LTC_PRE; ++i) {
@@ -385,7 +393,7 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
             const int kk = x / pieces, c = x - kk * pieces;
             const int key = k0 + kk;
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (key <= pos_hi) {
+            if (key <= pos_hi && key >= key_lo) {
                 const size_t slot = (size_t)table[key / page_size] * page_size + key % page_size;
                 val = c < lat_chunks ? reinterpret_cast<const uint4*>(lat + slot * L)[c]
                                      : reinterpret_cast<const uint4*>(kr + slot * R)[c - lat_chunks];
@@ -418,8 +426,10 @@ latent_attend_tc_kernel(const float* __restrict__ q_lat, long q_ts, long q_hs, c
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = k0 + 8 * j + 2 * t4 + e;
-                sc[j][e] = (row0 && key <= pos0 + g) ? sc[j][e] * scale : -INFINITY;
-                sc[j][2 + e] = (row1 && key <= pos0 + g + 8) ? sc[j][2 + e] * scale : -INFINITY;
+                const bool in0 = key <= pos0 + g && (window <= 0 || key > pos0 + g - window);
+                const bool in1 = key <= pos0 + g + 8 && (window <= 0 || key > pos0 + g + 8 - window);
+                sc[j][e] = (row0 && in0) ? sc[j][e] * scale : -INFINITY;
+                sc[j][2 + e] = (row1 && in1) ? sc[j][2 + e] * scale : -INFINITY;
                 mx0 = fmaxf(mx0, sc[j][e]);
                 mx1 = fmaxf(mx1, sc[j][2 + e]);
             }
@@ -513,8 +523,9 @@ VOB_EXPORT int vob_latent_attend_tc_supported(int H, int L, int R) {
 VOB_EXPORT int vob_latent_attend_tc(const float* q_lat, long q_ts, long q_hs, const float* q_rot, const void* lat, const void* kr,
                                     const int* block_tables, int max_pages, const int* seq_starts, const int* positions, int page_size,
                                     int seqs, int max_new, int H, int L, int R, float scale, void* out, long o_ts, long o_hs,
-                                    cudaStream_t stream) {
+                                    int window, cudaStream_t stream) {
     if (seqs <= 0 || max_new <= 0) return 0;
+    if (window < 0) return VOB_ERR_BAD_ARG;
     int wph, colsw;
     const int hb = ltc_shape(H, L, R, &wph, &colsw);
     if (hb <= 0) return VOB_ERR_UNSUPPORTED;
@@ -529,7 +540,7 @@ VOB_EXPORT int vob_latent_attend_tc(const float* q_lat, long q_ts, long q_hs, co
         if (e != cudaSuccess) return (int)e;                                                                                    \
         return vob_launch(latent_attend_tc_kernel<N>, grid, block, smem, stream, q_lat, q_ts, q_hs, q_rot, (const __nv_bfloat16*)lat, \
                           (const __nv_bfloat16*)kr, block_tables, max_pages, seq_starts, positions, page_size, H, L, R, scale,  \
-                          (__nv_bfloat16*)out, o_ts, o_hs, wph, colsw);                                                         \
+                          (__nv_bfloat16*)out, o_ts, o_hs, wph, colsw, window);                                                 \
     } while (0)
     if (colsw <= 64) VOB_LTC(4);
     if (colsw <= 128) VOB_LTC(8);

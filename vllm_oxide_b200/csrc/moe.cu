@@ -229,6 +229,14 @@ VOB_EXPORT int vob_moe_align(const int* idx, int P, int E, int* sorted, int cap,
 // w_gu [E, 2 ff, width]: an expert's gate rows, then its up rows. act 0: silu.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ float moe_silu(float g) { return g / (1.0f + expf(-g)); }
+// The gate on a hidden value. act 0: silu(g) * u. act 1 (clamped): g' = min(g, limit), u' = clamp(u, -limit, limit),
+// g' * sigmoid(1.702 g') * (u' + 1).
+__device__ __forceinline__ float moe_gate(float g, float u, int act, float limit) {
+    if (act == 0) return moe_silu(g) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
 // a float32 sum as the activations' type holds it
 template <typename T> __device__ __forceinline__ float moe_rounded(float v);
 template <> __device__ __forceinline__ float moe_rounded<float>(float v) { return v; }
@@ -237,7 +245,7 @@ template <> __device__ __forceinline__ float moe_rounded<__nv_bfloat16>(float v)
 template <typename T>
 __global__ void __launch_bounds__(256, 2)
 moe_gate_up_kernel(const T* __restrict__ x, long ld_x, const T* __restrict__ w_gu, const int* __restrict__ sorted,
-                   const int* __restrict__ tile_expert, int top, int width, int ff, T* __restrict__ h_out) {
+                   const int* __restrict__ tile_expert, int top, int width, int ff, T* __restrict__ h_out, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait(73);
     const int tile = blockIdx.x;
@@ -283,7 +291,7 @@ moe_gate_up_kernel(const T* __restrict__ x, long ld_x, const T* __restrict__ w_g
         for (int j = 0; j < 2; ++j) {
             const int c = col0 + tx + 16 * j;
             // the two products are rounded to the activations' type before the gate, as separate products would be
-            if (c < ff) st_f(h_out + (size_t)p * ff + c, moe_silu(moe_rounded<T>(g[i][j])) * moe_rounded<T>(u[i][j]));
+            if (c < ff) st_f(h_out + (size_t)p * ff + c, moe_gate(moe_rounded<T>(g[i][j]), moe_rounded<T>(u[i][j]), act, limit));
         }
     }
 }
@@ -386,7 +394,7 @@ __device__ __forceinline__ void moe_stage_rows(__nv_bfloat16 (*dst)[VOB_MOE_LDS]
 __global__ void __launch_bounds__(128)
 moe_gate_up_tc_kernel(const __nv_bfloat16* __restrict__ x, long ld_x, const __nv_bfloat16* __restrict__ w_gu,
                       const int* __restrict__ sorted, const int* __restrict__ tile_expert, int top, int width, int ff,
-                      __nv_bfloat16* __restrict__ h_out) {
+                      __nv_bfloat16* __restrict__ h_out, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait(75);
     const int tile = blockIdx.x;
@@ -446,7 +454,7 @@ moe_gate_up_tc_kernel(const __nv_bfloat16* __restrict__ x, long ld_x, const __nv
             if (p >= 0 && col < ff) {
                 const float gr = __bfloat162float(__float2bfloat16_rn(Cs[warp][0][el]));
                 const float ur = __bfloat162float(__float2bfloat16_rn(Cs[warp][1][el]));
-                h_out[(size_t)p * ff + col] = __float2bfloat16_rn(moe_silu(gr) * ur);
+                h_out[(size_t)p * ff + col] = __float2bfloat16_rn(moe_gate(gr, ur, act, limit));
             }
         }
         __syncwarp();
@@ -530,7 +538,7 @@ template <int BM, int STAGES, bool DOWN>
 __global__ void __launch_bounds__(BM == 128 ? 256 : 128)
 moe_pipe_kernel(const __nv_bfloat16* __restrict__ a, long ld_a, int a_div, const __nv_bfloat16* __restrict__ w,
                 const int* __restrict__ sorted, const int* __restrict__ tile_expert, const float* __restrict__ pair_w,
-                int K, int N, void* __restrict__ out) {
+                int K, int N, void* __restrict__ out, int act, float limit) {
     pdl_launch_dependents();
     pdl_wait(DOWN ? 76 : 75);
     constexpr int WR = BM == 128 ? 2 : 1;             // warps along the rows
@@ -635,7 +643,7 @@ moe_pipe_kernel(const __nv_bfloat16* __restrict__ a, long ld_a, int a_div, const
                 if (col < N) {
                     const float gr = __bfloat162float(__float2bfloat16_rn(Cs[el]));
                     const float ur = __bfloat162float(__float2bfloat16_rn(Cs[256 + el]));
-                    reinterpret_cast<__nv_bfloat16*>(out)[(size_t)p * N + col] = __float2bfloat16_rn(moe_silu(gr) * ur);
+                    reinterpret_cast<__nv_bfloat16*>(out)[(size_t)p * N + col] = __float2bfloat16_rn(moe_gate(gr, ur, act, limit));
                 }
             }
         }
@@ -645,7 +653,7 @@ moe_pipe_kernel(const __nv_bfloat16* __restrict__ a, long ld_a, int a_div, const
 
 template <int BM, int STAGES, bool DOWN>
 static int moe_pipe_launch(dim3 grid, cudaStream_t stream, const __nv_bfloat16* a, long ld_a, int a_div, const __nv_bfloat16* w,
-                           const int* sorted, const int* tile_expert, const float* pair_w, int K, int N, void* out) {
+                           const int* sorted, const int* tile_expert, const float* pair_w, int K, int N, void* out, int act = 0, float limit = 0.f) {
     const size_t smem = (size_t)STAGES * (BM + 128) * VOB_MOE_PLD * sizeof(__nv_bfloat16);
     static bool raised = false;
     if (!raised) {
@@ -654,7 +662,7 @@ static int moe_pipe_launch(dim3 grid, cudaStream_t stream, const __nv_bfloat16* 
         raised = true;
     }
     return vob_launch(moe_pipe_kernel<BM, STAGES, DOWN>, grid, dim3(BM == 128 ? 256 : 128), smem, stream, a, ld_a, a_div, w, sorted,
-                      tile_expert, pair_w, K, N, out);
+                      tile_expert, pair_w, K, N, out, act, limit);
 }
 
 static inline bool moe_rows_by16(const void* p, long ld, int K) { return K % 8 == 0 && ld % 8 == 0 && (((uintptr_t)p) & 15) == 0; }
@@ -663,9 +671,10 @@ static inline bool moe_rows_by16(const void* p, long ld, int K) { return K % 8 =
 // of a tile as the ordering made them (32; 128 only with the pipelined form). `max_tiles` = rows of `sorted` / tile_rows: the
 // grid covers them all and tiles behind the last one in use leave at once.
 VOB_EXPORT int vob_moe_gate_up(const void* x, int code, long ld_x, const void* w_gu, const int* sorted, const int* tile_expert,
-                               int max_tiles, int tile_rows, int top, int width, int ff, void* h_out, int tensor_cores, cudaStream_t stream) {
+                               int max_tiles, int tile_rows, int top, int width, int ff, void* h_out, int tensor_cores, int act, float limit,
+                               cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
-    if (top <= 0 || width <= 0 || ff <= 0) return VOB_ERR_BAD_ARG;
+    if (top <= 0 || width <= 0 || ff <= 0 || (act != 0 && act != 1)) return VOB_ERR_BAD_ARG;
     if (tile_rows != VOB_MOE_BM && !(tile_rows == 128 && tensor_cores)) return VOB_ERR_BAD_ARG;
     if (tensor_cores) {
         if (code != VOB_BF16) return VOB_ERR_BAD_ARG;
@@ -673,16 +682,16 @@ VOB_EXPORT int vob_moe_gate_up(const void* x, int code, long ld_x, const void* w
         const dim3 grid(max_tiles, (ff + 63) / 64);
         const __nv_bfloat16 *xa = (const __nv_bfloat16*)x, *wa = (const __nv_bfloat16*)w_gu;
         if (moe_rows_by16(x, ld_x, width) && moe_rows_by16(w_gu, width, width)) {
-            if (tile_rows == 128) return moe_pipe_launch<128, 3, false>(grid, stream, xa, ld_x, top, wa, sorted, tile_expert, nullptr, width, ff, h_out);
-            return moe_pipe_launch<32, 4, false>(grid, stream, xa, ld_x, top, wa, sorted, tile_expert, nullptr, width, ff, h_out);
+            if (tile_rows == 128) return moe_pipe_launch<128, 3, false>(grid, stream, xa, ld_x, top, wa, sorted, tile_expert, nullptr, width, ff, h_out, act, limit);
+            return moe_pipe_launch<32, 4, false>(grid, stream, xa, ld_x, top, wa, sorted, tile_expert, nullptr, width, ff, h_out, act, limit);
         }
         if (tile_rows != VOB_MOE_BM) return VOB_ERR_UNSUPPORTED;
         return vob_launch(moe_gate_up_tc_kernel, grid, dim3(128), 0, stream, xa, ld_x, wa, sorted, tile_expert, top, width, ff,
-                          (__nv_bfloat16*)h_out);
+                          (__nv_bfloat16*)h_out, act, limit);
     }
     if ((ff + 31) / 32 > 65535) return VOB_ERR_UNSUPPORTED;
     VOB_DISPATCH_ELEM(code, return vob_launch(moe_gate_up_kernel<ElemT>, dim3(max_tiles, (ff + 31) / 32), dim3(256), 0, stream, (const ElemT*)x,
-                                              ld_x, (const ElemT*)w_gu, sorted, tile_expert, top, width, ff, (ElemT*)h_out));
+                                              ld_x, (const ElemT*)w_gu, sorted, tile_expert, top, width, ff, (ElemT*)h_out, act, limit));
     return 0;
 }
 
@@ -710,12 +719,14 @@ VOB_EXPORT int vob_moe_down(const void* h, int code, const void* w_down, const i
 }
 
 // ---------------------------------------------------------------------------------------------
-// out[t, c] = sum_k y[t * top + k, c] over the token's choices in their order (k ascending), in the activations' type;
+// out[t, c] = sum_k y[t * top + k, c] over the token's choices in their order (k ascending) (+ shared[t, c] * sigmoid(shared_gate[t]),
+// where a shared expert's result [T, width] and its gate, one number per token `ld_gate` apart, are given), in the activations' type;
 // a token without choices (padding) gets zeros. Grid (tokens, ceil(width / 256)).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ idx, int top, int width, T* __restrict__ out) {
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ idx, int top, int width, T* __restrict__ out,
+                   const T* __restrict__ shared, const T* __restrict__ shared_gate, long ld_gate) {
     pdl_launch_dependents();
     pdl_wait(77);
     const int t = blockIdx.x, c = blockIdx.y * 256 + threadIdx.x;
@@ -723,13 +734,19 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ idx, int
     float acc = 0.f;
     for (int k = 0; k < top; ++k)
         if (idx[(size_t)t * top + k] >= 0) acc += y[((size_t)t * top + k) * width + c];
+    if (shared) {       // an expert every token uses, times the sigmoid of one number per token
+        float sv = ld_f(shared + (size_t)t * width + c);
+        if (shared_gate) sv *= 1.0f / (1.0f + expf(-ld_f(shared_gate + (size_t)t * ld_gate)));
+        acc += sv;
+    }
     st_f(out + (size_t)t * width + c, acc);
 }
 
-VOB_EXPORT int vob_moe_combine(const float* y, const int* idx, int T, int top, int width, void* out, int code, cudaStream_t stream) {
+VOB_EXPORT int vob_moe_combine(const float* y, const int* idx, int T, int top, int width, void* out, int code, const void* shared,
+                               const void* shared_gate, long ld_gate, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (top <= 0 || width <= 0 || (width + 255) / 256 > 65535) return VOB_ERR_BAD_ARG;
     VOB_DISPATCH_ELEM(code, return vob_launch(moe_combine_kernel<ElemT>, dim3(T, (width + 255) / 256), dim3(256), 0, stream, y, idx, top, width,
-                                              (ElemT*)out));
+                                              (ElemT*)out, (const ElemT*)shared, (const ElemT*)shared_gate, ld_gate));
     return 0;
 }

@@ -4,6 +4,8 @@
 //     mode 0 (delta rule with decay):  S_t = diag(w_t) S_(t-1) - b_t (u_t^T S_(t-1)) + k_t v_t^T
 //     mode 1 (fixed decay per head):   S_t = d_h S_(t-1) + k_t v_t^T
 //     mode 2 (gated delta rule):       S' = diag(w_t) S_(t-1);  S_t = S' + k_t (b_t (v_t - S'^T k_t))^T
+//     mode 3 (state space):            S_t = b_t S_(t-1) + k_t (u_t v_t)^T     (b_t a decay, u_t a step size: one number
+//                                      per token and head each; heads may share r and k in groups, as in mode 2)
 //     o_t = S_t^T r_t
 // w_t, b_t, u_t are float32 vectors per token, head and key channel, prepared by vob_delta_prep (or
 // by anything else that writes them); d_h is one number per head; in mode 2 b_t is one number per token
@@ -269,6 +271,132 @@ VOB_EXPORT int vob_conv_state_update(const void* proj, int code, long ld, int x_
 }
 
 // ---------------------------------------------------------------------------------------------
+// A short causal convolution over time on each channel, with the last taps - 1 inputs of a request kept in its state slot:
+//   y[t, c] = (bias[c]) + sum_j w[c, j] * x[t - taps + 1 + j, c]      (x before this step's rows comes from the state,
+//                                                                     which is zero at a request's start)
+//   out[t, c] = act(y + (residual ? x[t, c] : 0)),   act: 0 none, 1 silu
+// x is a column range of a projection output [T, ld] in the activations' type; out [T, ld_out] of type TO. The state is
+// only read here: vob_conv_state_update moves it on behind this kernel. Rows with a negative position (padding) get zeros.
+// Launch: grid (tokens, ceil(C / 128)), 128 threads, one channel each; the sum runs over the taps in order.
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename TO>
+__global__ void __launch_bounds__(128)
+causal_conv_kernel(const T* __restrict__ x, long ld, int C, int taps, const float* __restrict__ w, const float* __restrict__ bias,
+                   const float* __restrict__ cstate, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                   const int* __restrict__ seq_starts, const int* __restrict__ state_slots, int residual, int act,
+                   TO* __restrict__ out, long ld_out) {
+    pdl_launch_dependents();
+    pdl_wait(49);
+    const int t = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
+    if (c >= C) return;
+    if (positions[t] < 0) {
+        st_f(out + (size_t)t * ld_out + c, 0.f);
+        return;
+    }
+    const int s = row_seq[t];
+    const int i = t - seq_starts[s];                 // this row's place among the request's rows of the step
+    const float* st = cstate ? cstate + (size_t)state_slots[s] * (taps - 1) * C : nullptr;
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        const float v = i - back >= 0 ? ld_f(x + (size_t)(t - back) * ld + c) : st[(size_t)(taps - 1 + i - back) * C + c];
+        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+    }
+    if (residual) acc += ld_f(x + (size_t)t * ld + c);
+    if (act == 1) acc = acc / (1.0f + expf(-acc));
+    st_f(out + (size_t)t * ld_out + c, acc);
+}
+
+VOB_EXPORT int vob_causal_conv(const void* x, int code, long ld, int C, int taps, const float* w, const float* bias, const float* cstate,
+                               const int* positions, const int* row_seq, const int* seq_starts, const int* state_slots, int residual,
+                               int act, void* out, int out_code, long ld_out, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (C <= 0 || taps < 1 || !w || (taps > 1 && !cstate) || (act != 0 && act != 1) || (C + 127) / 128 > 65535) return VOB_ERR_BAD_ARG;
+    const dim3 grid(T, (C + 127) / 128);
+#define VOB_CONV(T_, TO_)                                                                                                     \
+    return vob_launch(causal_conv_kernel<T_, TO_>, grid, dim3(128), 0, stream, (const T_*)x, ld, C, taps, w, bias, cstate, positions, \
+                      row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out)
+    if (code == VOB_F32 && out_code == VOB_F32) VOB_CONV(float, float);
+    if (code == VOB_BF16 && out_code == VOB_BF16) VOB_CONV(__nv_bfloat16, __nv_bfloat16);
+    if (code == VOB_BF16 && out_code == VOB_F32) VOB_CONV(__nv_bfloat16, float);
+#undef VOB_CONV
+    return VOB_ERR_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Step sizes and decays of a state-space mixer, per token and head, float32:
+//   dt = softplus(raw + dt_bias[h]) (no clamp);   decay = exp(-exp(A_log[h]) * dt)
+// raw: H columns of a projection output [T, ld]. Launch: ceil(T * H / 256) blocks of 256 threads.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssm_steps_kernel(const T* __restrict__ raw, long ld, const float* __restrict__ dt_bias, const float* __restrict__ a_log, int T_rows,
+                 int H, float* __restrict__ dt_out, float* __restrict__ decay_out) {
+    pdl_launch_dependents();
+    pdl_wait(50);
+    const long long e = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (e >= (long long)T_rows * H) return;
+    const int t = (int)(e / H), h = (int)(e % H);
+    const float z = ld_f(raw + (size_t)t * ld + h) + dt_bias[h];
+    const float dt = z > 20.f ? z : log1pf(expf(z));       // beyond 20 the two agree to the last bit of a float
+    dt_out[e] = dt;
+    decay_out[e] = expf(-expf(a_log[h]) * dt);
+}
+
+VOB_EXPORT int vob_ssm_steps(const void* raw, int code, long ld, const float* dt_bias, const float* a_log, int T, int H, float* dt_out,
+                             float* decay_out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || !dt_bias || !a_log) return VOB_ERR_BAD_ARG;
+    const long long n = (long long)T * H;
+    VOB_DISPATCH_ELEM(code, return vob_launch(ssm_steps_kernel<ElemT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                                              (const ElemT*)raw, ld, dt_bias, a_log, T, H, dt_out, decay_out));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Behind a state-space scan, per token: y = (o + skip[h] * x) * silu(z), then an RMS norm over each of `groups` equal
+// parts of the row (each part by its own root mean square), times weight: the gate comes before the norm.
+// o float32 [T, n]; x float32 columns of [T, ld_x]; z columns of a projection output [T, ld_z] in the activations' type;
+// skip float32 [H] (one number per head of n / H features); weight float32 [n]; out [T, n] in the activations' type.
+// Launch: grid (tokens, groups), 128 threads.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+ssm_post_kernel(const float* __restrict__ o, const float* __restrict__ x, long ld_x, const T* __restrict__ z, long ld_z,
+                const float* __restrict__ skip, const float* __restrict__ weight, float eps, int n, int H, int groups,
+                T* __restrict__ out, long ld_out) {
+    pdl_launch_dependents();
+    pdl_wait(51);
+    __shared__ float red[4];
+    extern __shared__ float yrow[];
+    const int t = blockIdx.x, gsz = n / groups, c0 = blockIdx.y * gsz, hv = n / H, tid = threadIdx.x;
+    float ss = 0.f;
+    for (int c = tid; c < gsz; c += 128) {
+        const int f = c0 + c;
+        const float zv = ld_f(z + (size_t)t * ld_z + f);
+        const float y = fmaf(skip[f / hv], x[(size_t)t * ld_x + f], o[(size_t)t * n + f]) * (zv / (1.0f + expf(-zv)));
+        yrow[c] = y;
+        ss = fmaf(y, y, ss);
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    const float inv = 1.0f / sqrtf(((red[0] + red[1]) + (red[2] + red[3])) / (float)gsz + eps);
+    for (int c = tid; c < gsz; c += 128) st_f(out + (size_t)t * ld_out + c0 + c, yrow[c] * inv * weight[c0 + c]);
+}
+
+VOB_EXPORT int vob_ssm_post(const float* o, const float* x, long ld_x, const void* z, int code, long ld_z, const float* skip,
+                            const float* weight, float eps, int T, int n, int H, int groups, void* out, long ld_out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (n <= 0 || H <= 0 || groups <= 0 || n % H || n % groups || groups > 65535 || !skip || !weight) return VOB_ERR_BAD_ARG;
+    const size_t smem = (size_t)(n / groups) * sizeof(float);
+    if (smem > 40 * 1024) return VOB_ERR_UNSUPPORTED;
+    VOB_DISPATCH_ELEM(code, return vob_launch(ssm_post_kernel<ElemT>, dim3(T, groups), dim3(128), smem, stream, o, x, ld_x, (const ElemT*)z,
+                                              ld_z, skip, weight, eps, n, H, groups, (ElemT*)out, ld_out));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Rotary positions and a scale, to float32: for every head of D features, feature i < rot / 2 is
 // paired with feature i + rot / 2 and the pair (a, b) becomes (a cos - b sin, b cos + a sin) with
 // the angle float(position) * inv_freq[i]; features from `rot` on pass unchanged; everything is
@@ -334,7 +462,7 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
     // t takes elements t, t + 128, ... of it (NPT per token), and the list of the next CT tokens is fetched into
     // registers while the staged tokens are worked on. The chain from token to token is what bounds a long portion.
     constexpr int KPAD = KS * KPT, VT = 128 / KS, NA = MODE == 0 ? 5 : MODE == 2 ? 3 : 2;
-    constexpr int NB = MODE == 2 ? 1 : 0;          // mode 2: one more element per token, the writing strength
+    constexpr int NB = MODE == 2 ? 1 : MODE == 3 ? 2 : 0;   // mode 2: one more element per token, the writing strength; mode 3: decay and step size
     // Lane q of a column holds key channels q * KPT .. q * KPT + KPT - 1. In shared memory a lane's channels lie
     // together (read four at a time), each lane's group padded by four floats so that the KS groups fall into
     // different banks: channel c of an array at (c / KPT) * (KPT + 4) + c % KPT.
@@ -386,6 +514,8 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
                         }
                     } else if (x == NA * KPAD + VT) {
                         val = raw_ld(b + row * H + h);
+                    } else if (MODE == 3 && x == NA * KPAD + VT + 1) {
+                        val = raw_ld(u + row * H + h);
                     } else {
                         const int jv = blockIdx.x * VT + (x - NA * KPAD);
                         if (jv < V) val = raw_ld(v + row * ld_v + h * V + jv);
@@ -412,6 +542,8 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
                     sm[tt * PER + NA * KPADP + (x - NA * KPAD)] = raw_to_float<TV>(pre[tt * NPT + i]);
                 } else if (NB && x == NA * KPAD + VT) {
                     sm[tt * PER + NA * KPADP + VT] = __uint_as_float(pre[tt * NPT + i]);
+                } else if (NB == 2 && x == NA * KPAD + VT + 1) {
+                    sm[tt * PER + NA * KPADP + VT + 1] = __uint_as_float(pre[tt * NPT + i]);
                 }
             }
         __syncthreads();
@@ -489,6 +621,10 @@ recurrence_scan_kernel(const TRK* __restrict__ r, long ld_r, const TRK* __restri
                 for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], uu, S[i]);
                 if (q == 0 && col) o[(size_t)(c0 + tt) * H * V + h * V + j] = fmaf(rk, uu, read);
                 continue;
+            } else if (MODE == 3) {
+                const float a = sm[tt * PER + NA * KPADP + VT], dv = sm[tt * PER + NA * KPADP + VT + 1] * vj;
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], dv, a * S[i]);
             } else {
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) S[i] = fmaf(kk[i], vj, decay * S[i]);
@@ -542,7 +678,8 @@ VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const voi
     if (mode == 0 && (!w || !b || !u)) return VOB_ERR_BAD_ARG;
     if (mode == 1 && !w) return VOB_ERR_BAD_ARG;
     if (mode == 2 && (!w || !b)) return VOB_ERR_BAD_ARG;
-    if (rk_div <= 0 || H % rk_div != 0 || (mode != 2 && rk_div != 1)) return VOB_ERR_BAD_ARG;
+    if (mode == 3 && (!b || !u)) return VOB_ERR_BAD_ARG;
+    if (rk_div <= 0 || H % rk_div != 0 || (mode != 2 && mode != 3 && rk_div != 1)) return VOB_ERR_BAD_ARG;
     // conv_x (mode 2, optional): columns of the activations' type (v's) whose last conv_taps - 1 rows per request are
     // left in conv_state [slots, conv_taps - 1, conv_c]
     if (conv_x && (mode != 2 || conv_c <= 0 || conv_taps < 2 || !conv_state)) return VOB_ERR_BAD_ARG;
@@ -553,6 +690,7 @@ VOB_EXPORT int vob_recurrence_scan(int mode, const void* r, long ld_r, const voi
     if (mode == 1 && rk_code == VOB_F32 && v_code == VOB_BF16) return scan_launch<1, float, __nv_bfloat16>(VOB_ARGS);
     if (mode == 2 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<2, float, float>(VOB_ARGS);
     if (mode == 2 && rk_code == VOB_F32 && v_code == VOB_BF16) return scan_launch<2, float, __nv_bfloat16>(VOB_ARGS);
+    if (mode == 3 && rk_code == VOB_F32 && v_code == VOB_F32) return scan_launch<3, float, float>(VOB_ARGS);
 #undef VOB_ARGS
     return VOB_ERR_BAD_ARG;
 }

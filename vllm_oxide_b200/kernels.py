@@ -257,7 +257,7 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
 
 
 @_timed
-def layernorm_add(resid: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+def layernorm_add(resid: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,
                   copy: Optional[torch.Tensor] = None) -> None:
     """resid += LN(delta) with LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * weight + bias; `copy` ([T, h] in the
     activations' type), if given, receives the new residual."""
@@ -280,7 +280,7 @@ def layernorm_add(resid: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor
 
 
 @_timed
-def layernorm_rows(resid: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+def layernorm_rows(resid: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
                    rows: Optional[torch.Tensor] = None) -> None:
     """out[r] = LN(resid[rows[r]]) (every row in order without `rows`); the residual is left as it is."""
     op = "layernorm_rows"
@@ -919,7 +919,9 @@ def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     mode 0: S = diag(w_t) S - b_t (u_t^T S) + k_t v_t^T with w, b, u float32 [T, heads * K];
     mode 1: S = w[h] S + k_t v_t^T with w float32 [heads];
     mode 2: S' = diag(w_t) S; S = S' + k_t (b_t (v_t - S'^T k_t))^T with w float32 [T, heads * K], b float32
-    [T, heads], and r, k float32 [T, rk_heads * K] (head h reads r and k of head h // (heads / rk_heads)).
+    [T, heads], and r, k float32 [T, rk_heads * K] (head h reads r and k of head h // (heads / rk_heads));
+    mode 3: S = b_t S + k_t (u_t v_t)^T with b (a decay) and u (a step size) float32 [T, heads], r, k, v float32, heads
+    sharing r and k as in mode 2.
     o_t = S^T r_t -> out float32 [T, heads * V].
     state float32 [slots, heads, K, V]; r, k [T, heads * K] and v [T, heads * V] with any row stride.
     Mode 2 with `conv_x` ([T, C] of v's type, any row stride) and `conv_state` (float32 [slots, taps - 1, C]) also does
@@ -933,7 +935,7 @@ def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     K, V = state.shape[2], state.shape[3]
     T = r.shape[0]
     rk_heads = heads if rk_heads is None else int(rk_heads)
-    if rk_heads <= 0 or heads % rk_heads != 0 or (mode != 2 and rk_heads != heads):
+    if rk_heads <= 0 or heads % rk_heads != 0 or (mode not in (2, 3) and rk_heads != heads):
         raise ShapeError(op, f"{heads} heads cannot share the r and k of {rk_heads} heads in mode {mode}")
     if r.shape != (T, rk_heads * K) or k.shape != (T, rk_heads * K) or v.shape != (T, heads * V) or r.dtype != k.dtype:
         raise ShapeError(op, f"r, k [{T}, {rk_heads * K}] and v [{T}, {heads * V}] are needed, got {list(r.shape)}, {list(k.shape)}, {list(v.shape)}")
@@ -952,6 +954,12 @@ def recurrence_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor
             raise ShapeError(op, f"w must be contiguous float32 [{T}, {heads * K}]")
         if b is None or b.dtype != torch.float32 or b.shape != (T, heads) or not b.is_contiguous():
             raise ShapeError(op, f"b must be contiguous float32 [{T}, {heads}]")
+    elif mode == 3:
+        if r.dtype != torch.float32 or v.dtype != torch.float32:
+            raise ShapeError(op, f"mode 3 takes float32 r, k and v, got {r.dtype} and {v.dtype}")
+        for name, t in (("b", b), ("u", u)):
+            if t is None or t.dtype != torch.float32 or t.shape != (T, heads) or not t.is_contiguous():
+                raise ShapeError(op, f"{name} must be contiguous float32 [{T}, {heads}]")
     else:
         raise ShapeError(op, f"mode {mode} is not known")
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
@@ -1065,9 +1073,118 @@ def conv_state_update(proj: torch.Tensor, x_off: int, conv_state: torch.Tensor, 
              _ptr(state_slots), num_seqs, _stream()), op)
 
 
+@_timed
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], conv_state: Optional[torch.Tensor],
+                positions: torch.Tensor, row_seq: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
+                out: torch.Tensor, residual: bool = False, act: str = "none") -> None:
+    """A short causal convolution over time on each channel: y[t, c] = bias[c] + sum_j weight[c, j] * x[t - taps + 1 + j, c],
+    inputs before the step's rows taken from `conv_state` (float32 [slots, taps - 1, C], the request's last inputs; zero at its
+    start); out = act(y + x) with `residual`, act(y) without; act "none" or "silu". x [T, C] (a column range of a projection,
+    any row stride), out [T, C] in x's type or float32. The state is only read: `conv_state_update` moves it on afterwards."""
+    op = "causal_conv"
+    _cuda(op, x, weight, bias, conv_state, positions, row_seq, seq_starts, state_slots, out)
+    _rows_2d(x, op, "x")
+    _rows_2d(out, op, "out")
+    T, C = x.shape
+    if weight.dtype != torch.float32 or weight.dim() != 2 or weight.shape[0] != C or not weight.is_contiguous():
+        raise ShapeError(op, f"weight must be contiguous float32 [{C}, taps], got {weight.dtype} {list(weight.shape)}")
+    taps = weight.shape[1]
+    _f32_vec(bias, C, op, "bias")
+    if taps > 1 and (conv_state is None or conv_state.dtype != torch.float32 or conv_state.dim() != 3 or not conv_state.is_contiguous()
+                     or conv_state.shape[1:] != (taps - 1, C)):
+        raise ShapeError(op, f"conv_state must be contiguous float32 [slots, {taps - 1}, {C}]")
+    if out.shape != (T, C) or out.dtype not in (x.dtype, torch.float32):
+        raise ShapeError(op, f"out must be [{T}, {C}] of x's type or float32, got {out.dtype} {list(out.shape)}")
+    if act not in ("none", "silu"):
+        raise ShapeError(op, f"act {act!r} is not known (none or silu)")
+    _int32_vec(positions, T, op, "positions")
+    _int32_vec(row_seq, T, op, "row_seq")
+    _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
+    _int32_vec(state_slots, num_seqs, op, "state_slots")
+    f = _fn("recurrence", "vob_causal_conv", [_P, _I, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _L, _I, _P])
+    _check(f(_ptr(x), _code(x, op), x.stride(0), C, taps, _ptr(weight), _ptr(bias), _ptr(conv_state) if taps > 1 else _P(0),
+             _ptr(positions), _ptr(row_seq), _ptr(seq_starts), _ptr(state_slots), 1 if residual else 0, 1 if act == "silu" else 0,
+             _ptr(out), _code(out, op), out.stride(0), T, _stream()), op)
+
+
+@_timed
+def ssm_steps(raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, dt_out: torch.Tensor, decay_out: torch.Tensor) -> None:
+    """dt = softplus(raw + dt_bias[h]) and decay = exp(-exp(a_log[h]) * dt) per token and head, float32 [T, heads] each; raw
+    [T, heads] is a column range of a projection output."""
+    op = "ssm_steps"
+    _cuda(op, raw, dt_bias, a_log, dt_out, decay_out)
+    _rows_2d(raw, op, "raw")
+    T, H = raw.shape
+    _f32_vec(dt_bias, H, op, "dt_bias")
+    _f32_vec(a_log, H, op, "a_log")
+    for name, t in (("dt_out", dt_out), ("decay_out", decay_out)):
+        if t.dtype != torch.float32 or t.shape != (T, H) or not t.is_contiguous():
+            raise ShapeError(op, f"{name} must be contiguous float32 [{T}, {H}], got {t.dtype} {list(t.shape)}")
+    f = _fn("recurrence", "vob_ssm_steps", [_P, _I, _L, _P, _P, _I, _I, _P, _P, _P])
+    _check(f(_ptr(raw), _code(raw, op), raw.stride(0), _ptr(dt_bias), _ptr(a_log), T, H, _ptr(dt_out), _ptr(decay_out), _stream()), op)
+
+
+@_timed
+def ssm_post(o: torch.Tensor, x: torch.Tensor, z: torch.Tensor, skip: torch.Tensor, weight: torch.Tensor, eps: float, heads: int,
+             groups: int, out: torch.Tensor) -> None:
+    """out = rms_groups((o + skip[head] * x) * silu(z)) * weight: the gate first, then an RMS norm over each of `groups` equal
+    parts of the row. o float32 [T, n] contiguous; x float32 [T, n] (any row stride); z and out [T, n] in the activations' type
+    (any row stride); skip float32 [heads]; weight float32 [n]."""
+    op = "ssm_post"
+    _cuda(op, o, x, z, skip, weight, out)
+    _rows_2d(x, op, "x")
+    _rows_2d(z, op, "z")
+    _rows_2d(out, op, "out")
+    if o.dtype != torch.float32 or o.dim() != 2 or not o.is_contiguous():
+        raise ShapeError(op, f"o must be contiguous float32 [T, n], got {o.dtype} {list(o.shape)}")
+    T, n = o.shape
+    if x.shape != (T, n) or x.dtype != torch.float32 or z.shape != (T, n) or out.shape != (T, n) or out.dtype != z.dtype:
+        raise ShapeError(op, f"x float32, z and out of one type, all [{T}, {n}], are needed")
+    if heads <= 0 or groups <= 0 or n % heads or n % groups:
+        raise ShapeError(op, f"{n} features do not split into {heads} heads and {groups} groups")
+    _f32_vec(skip, heads, op, "skip")
+    _f32_vec(weight, n, op, "weight")
+    f = _fn("recurrence", "vob_ssm_post", [_P, _P, _L, _P, _I, _L, _P, _P, _F, _I, _I, _I, _I, _P, _L, _P])
+    _check(f(_ptr(o), _ptr(x), x.stride(0), _ptr(z), _code(z, op), z.stride(0), _ptr(skip), _ptr(weight), float(eps), T, n, int(heads),
+             int(groups), _ptr(out), out.stride(0), _stream()), op)
+
+
+@_timed
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float) -> None:
+    """out[t, j] = g * sigmoid(1.702 g) * (u + 1) with g = min(gate_up[t, j], limit), u = clamp(gate_up[t, I + j], -limit, limit)."""
+    op = "glu_clamped"
+    _cuda(op, gate_up, out)
+    _rows_2d(gate_up, op, "gate_up")
+    T, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (T, two_i // 2) or out.dtype != gate_up.dtype or not out.is_contiguous() or not limit > 0:
+        raise ShapeError(op, f"gate_up [{T}, 2 I], a contiguous out [{T}, I] of its type and a positive limit are needed, got "
+                             f"{list(gate_up.shape)}, {out.dtype} {list(out.shape)}, {limit}")
+    f = _fn("elementwise", "vob_glu_clamped", [_P, _L, _P, _I, _I, _I, _F, _P])
+    _check(f(_ptr(gate_up), gate_up.stride(0), _ptr(out), _code(out, op), T, two_i // 2, float(limit), _stream()), op)
+
+
+@_timed
+def depth_average(stack: torch.Tensor, x: torch.Tensor, weights: Optional[torch.Tensor], n: int) -> None:
+    """stack[:, n] = x; then, with `weights` (float32 [n + 1]), x = sum_j weights[j] * stack[:, j] over j = 0 .. n. Without
+    weights only the filing is done (slot 0 takes the embedding's output). stack float32 [T, slots, h], x float32 [T, h]."""
+    op = "depth_average"
+    _cuda(op, stack, x, weights)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise ShapeError(op, f"x must be contiguous float32 [T, h], got {x.dtype} {list(x.shape)}")
+    T, h = x.shape
+    if stack.dtype != torch.float32 or stack.dim() != 3 or stack.shape[0] != T or stack.shape[2] != h or not stack.is_contiguous():
+        raise ShapeError(op, f"stack must be contiguous float32 [{T}, slots, {h}], got {stack.dtype} {list(stack.shape)}")
+    if not 0 <= n < stack.shape[1]:
+        raise ShapeError(op, f"slot {n} lies outside the stack's {stack.shape[1]}")
+    _f32_vec(weights, n + 1, op, "weights")
+    f = _fn("elementwise", "vob_depth_average", [_P, _P, _P, _I, _I, _I, _I, _I, _P])
+    _check(f(_ptr(stack), _ptr(x), _ptr(weights), T, stack.shape[1], h, int(n), 0 if weights is not None else 1, _stream()), op)
+
+
 # ------------------------------------------------------------------------------------ mixture of experts
 MOE_TILE_ROWS = 32           # rows of a tile of (token, expert) pairs (VOB_MOE_BM of csrc/moe.cu)
 MOE_LARGE_TILE_ROWS = 128    # the pipelined tensor-core products also take tiles of this many
+MOE_ACTIVATIONS = {"silu": 0, "clamped_swish": 1}    # how an expert's gate acts on its hidden values
 MOE_LARGE_TILE_FROM = 64     # pairs an expert gets on average from which the large tiles are taken
 
 
@@ -1148,10 +1265,15 @@ def _moe_tiles(op, sorted_pairs, tile_expert, tile_rows, tensor_cores, width, ff
 
 @_timed
 def moe_gate_up(x: torch.Tensor, w_gu: torch.Tensor, sorted_pairs: torch.Tensor, tile_expert: torch.Tensor, top: int,
-                h_out: torch.Tensor, tensor_cores: bool = False, tile_rows: int = MOE_TILE_ROWS) -> None:
+                h_out: torch.Tensor, tensor_cores: bool = False, tile_rows: int = MOE_TILE_ROWS, activation: str = "silu",
+                limit: float = 0.0) -> None:
     """h_out[pair] = silu(W_gate[e] x[token]) * (W_up[e] x[token]) for every pair of the ordered list; w_gu [E, 2 ff, width]
-    (an expert's gate rows, then its up rows) and h_out [T * top, ff] of x's type. `tensor_cores`: the bfloat16 tile form."""
+    (an expert's gate rows, then its up rows) and h_out [T * top, ff] of x's type. `tensor_cores`: the bfloat16 tile form.
+    `activation` "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)."""
     op = "moe_gate_up"
+    if activation not in MOE_ACTIVATIONS or (activation == "clamped_swish" and not limit > 0):
+        raise ShapeError(op, f"activation {activation!r} (limit {limit}) is not known ({', '.join(MOE_ACTIVATIONS)}; the clamped one "
+                             f"needs a positive limit)")
     _cuda(op, x, w_gu, sorted_pairs, tile_expert, h_out)
     _rows_2d(x, op, "x")
     T, width = x.shape
@@ -1165,9 +1287,9 @@ def moe_gate_up(x: torch.Tensor, w_gu: torch.Tensor, sorted_pairs: torch.Tensor,
     tiles = _moe_tiles(op, sorted_pairs, tile_expert, tile_rows, tensor_cores, width, ff)
     if tile_rows != MOE_TILE_ROWS and (x.stride(0) % 8 or x.data_ptr() % 16):
         raise ShapeError(op, f"tiles of {tile_rows} rows need rows of x that start on 16-byte boundaries")
-    f = _fn("moe", "vob_moe_gate_up", [_P, _I, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _P])
+    f = _fn("moe", "vob_moe_gate_up", [_P, _I, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _F, _P])
     _check(f(_ptr(x), _code(x, op), x.stride(0), _ptr(w_gu), _ptr(sorted_pairs), _ptr(tile_expert), tiles, int(tile_rows), int(top), width, ff,
-             _ptr(h_out), 1 if tensor_cores else 0, _stream()), op)
+             _ptr(h_out), 1 if tensor_cores else 0, MOE_ACTIVATIONS[activation], float(limit), _stream()), op)
 
 
 @_timed
@@ -1196,10 +1318,19 @@ def moe_down(h: torch.Tensor, w_down: torch.Tensor, sorted_pairs: torch.Tensor, 
 
 
 @_timed
-def moe_combine(y: torch.Tensor, idx: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = sum over k, in order, of y[t * top + k] where idx[t, k] >= 0; out [T, width] in the activations' type."""
+def moe_combine(y: torch.Tensor, idx: torch.Tensor, out: torch.Tensor, shared: Optional[torch.Tensor] = None,
+                shared_gate: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum over k, in order, of y[t * top + k] where idx[t, k] >= 0; out [T, width] in the activations' type.
+    `shared` [T, width] (out's type): the result of an expert every token uses, added; `shared_gate` [T] (a column of a
+    projection output, out's type): `shared` is first multiplied by its sigmoid, token by token."""
     op = "moe_combine"
-    _cuda(op, y, idx, out)
+    _cuda(op, y, idx, out, shared, shared_gate)
+    if shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype or not shared.is_contiguous()):
+        raise ShapeError(op, f"shared must be contiguous {out.dtype} {list(out.shape)}, got {shared.dtype} {list(shared.shape)}")
+    if shared_gate is not None and (shared is None or shared_gate.dim() != 1 or shared_gate.shape[0] != out.shape[0]
+                                    or shared_gate.dtype != out.dtype):
+        raise ShapeError(op, f"shared_gate must be {out.dtype} [{out.shape[0]}] and go with shared, got {shared_gate.dtype} "
+                             f"{list(shared_gate.shape)}")
     if idx.dtype != torch.int32 or idx.dim() != 2 or not idx.is_contiguous():
         raise ShapeError(op, f"idx must be contiguous int32 [T, top], got {idx.dtype} {list(idx.shape)}")
     T, top = idx.shape
@@ -1207,8 +1338,9 @@ def moe_combine(y: torch.Tensor, idx: torch.Tensor, out: torch.Tensor) -> None:
         raise ShapeError(op, f"y must be contiguous float32 [{T * top}, width], got {y.dtype} {list(y.shape)}")
     if out.shape != (T, y.shape[1]) or not out.is_contiguous():
         raise ShapeError(op, f"out must be contiguous [{T}, {y.shape[1]}], got {list(out.shape)}")
-    f = _fn("moe", "vob_moe_combine", [_P, _P, _I, _I, _I, _P, _I, _P])
-    _check(f(_ptr(y), _ptr(idx), T, top, y.shape[1], _ptr(out), _code(out, op), _stream()), op)
+    f = _fn("moe", "vob_moe_combine", [_P, _P, _I, _I, _I, _P, _I, _P, _P, _L, _P])
+    _check(f(_ptr(y), _ptr(idx), T, top, y.shape[1], _ptr(out), _code(out, op), _ptr(shared), _ptr(shared_gate),
+             shared_gate.stride(0) if shared_gate is not None else 0, _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention over a latent cache
@@ -1244,12 +1376,13 @@ def latent_prep(proj: torch.Tensor, q_off: int, heads: int, dim: int, rot: int, 
 @_timed
 def latent_attend(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, kr: torch.Tensor, block_tables: torch.Tensor,
                   row_seq: torch.Tensor, positions: torch.Tensor, scale: float, out: torch.Tensor, splits: int = 1,
-                  partials: Optional[torch.Tensor] = None) -> None:
+                  partials: Optional[torch.Tensor] = None, window: int = 0) -> None:
     """Causal attention of every row over its request's latent pages: score = (q_lat . c + q_rot . kr) *
     scale, softmax in float32, out_lat = sum of weights * c. q_lat float32 and out (cache type) are
     indexed [T, heads, rank] through their strides (last stride 1); q_rot float32 [T, heads, rot].
     `splits` > 1 shares every row's keys over that many blocks; `partials` (float32, at least
-    T * heads * splits * (rank + 2) elements) is their scratch, and a second launch merges them."""
+    T * heads * splits * (rank + 2) elements) is their scratch, and a second launch merges them. `window` > 0: a row sees
+    itself and the window - 1 tokens before it."""
     op = "latent_attend"
     _cuda(op, q_lat, q_rot, lat, kr, block_tables, row_seq, positions, out)
     if q_lat.dim() != 3 or q_lat.dtype != torch.float32 or q_lat.stride(2) != 1:
@@ -1272,10 +1405,10 @@ def latent_attend(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, k
         _cuda(op, partials)
         if partials is None or partials.dtype != torch.float32 or not partials.is_contiguous() or partials.numel() < T * H * splits * (L + 2):
             raise ShapeError(op, f"{splits} splits need contiguous float32 partials of {T * H * splits * (L + 2)} elements")
-    f = _fn("latent_attention", "vob_latent_attend", [_P, _L, _L, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _L, _L, _I, _P, _P])
+    f = _fn("latent_attention", "vob_latent_attend", [_P, _L, _L, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _L, _L, _I, _P, _I, _P])
     _check(f(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), _ptr(lat), _ptr(kr), _code(lat, op), _ptr(block_tables),
              block_tables.shape[1], _ptr(row_seq), _ptr(positions), lat.shape[2], T, H, L, R, float(scale), _ptr(out), _code(out, op),
-             out.stride(0), out.stride(1), splits, _ptr(partials) if splits > 1 else _P(0), _stream()), op, 2 if splits > 1 else 1)
+             out.stride(0), out.stride(1), splits, _ptr(partials) if splits > 1 else _P(0), int(window), _stream()), op, 2 if splits > 1 else 1)
 
 
 def latent_attend_tc_supported(heads: int, rank: int, rot: int) -> bool:
@@ -1286,7 +1419,8 @@ def latent_attend_tc_supported(heads: int, rank: int, rot: int) -> bool:
 
 @_timed
 def latent_attend_tc(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor, kr: torch.Tensor, block_tables: torch.Tensor,
-                     seq_starts: torch.Tensor, positions: torch.Tensor, num_seqs: int, max_new: int, scale: float, out: torch.Tensor) -> None:
+                     seq_starts: torch.Tensor, positions: torch.Tensor, num_seqs: int, max_new: int, scale: float, out: torch.Tensor,
+                     window: int = 0) -> None:
     """`latent_attend` for prompt portions in bfloat16 on the tensor cores: request s owns rows seq_starts[s] ..
     seq_starts[s + 1] - 1 (consecutive positions), none more than `max_new`. Same operands and result."""
     op = "latent_attend_tc"
@@ -1309,10 +1443,10 @@ def latent_attend_tc(q_lat: torch.Tensor, q_rot: torch.Tensor, lat: torch.Tensor
         raise ShapeError(op, "block_tables must be contiguous int32 [requests, max_pages]")
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
     _int32_vec(positions, T, op, "positions")
-    f = _fn("latent_attention", "vob_latent_attend_tc", [_P, _L, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _L, _L, _P])
+    f = _fn("latent_attention", "vob_latent_attend_tc", [_P, _L, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P, _L, _L, _I, _P])
     _check(f(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), _ptr(lat), _ptr(kr), _ptr(block_tables), block_tables.shape[1],
              _ptr(seq_starts), _ptr(positions), lat.shape[2], int(num_seqs), int(max_new), H, L, R, float(scale), _ptr(out), out.stride(0),
-             out.stride(1), _stream()), op)
+             out.stride(1), int(window), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention with options
@@ -1331,16 +1465,21 @@ def flex_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, positions:
               inv_freq: Optional[torch.Tensor], rot: int, unit_rms: bool, eps: float, q_temp, vmix: Optional[torch.Tensor],
               v_first: Optional[torch.Tensor], v_mode: int, q_out: torch.Tensor, kcache: Optional[torch.Tensor],
               vcache: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int,
-              q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None) -> None:
+              q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None,
+              q_pre_w: Optional[torch.Tensor] = None, k_pre_w: Optional[torch.Tensor] = None) -> None:
     """Per token, from the columns q_off.., k_off.., v_off.. of `proj`: q and k with their first `rot` features rotated
     (feature i with i + rot / 2, by position * inv_freq[i]), then (unit_rms) divided by sqrt(mean(x^2) + eps) per head;
     q times 1 + coef * ln(floor((pos + 1) / every) + 1) for q_temp = (coef, every). q goes to q_out [T, heads * dim], k
     and v to their cache slots. v_mode 1 also leaves v in v_first [T, kv_heads * vdim]; v_mode 2 mixes
     v <- (1 - vmix) v + vmix v_first before the write (vmix: one float32 on the device). `q_norm_w`, `k_norm_w` (float32
-    [dim], shared by the heads) multiply q and k behind the division. Without caches (`kcache` None: a layer that reads
+    [dim], shared by the heads) multiply q and k behind the division. `q_pre_w` (float32 [heads * dim]) / `k_pre_w` (float32
+    [kv_heads * dim]): BEFORE the rotation the whole projection, all its heads at once, is divided by sqrt(mean(x^2) + eps) and
+    multiplied by that weight. Without caches (`kcache` None: a layer that reads
     what another layer cached) only q is prepared and `proj` needs no k and v columns."""
     op = "flex_prep"
-    _cuda(op, proj, positions, slots, inv_freq, vmix, v_first, q_out, kcache, vcache, q_norm_w, k_norm_w)
+    _cuda(op, proj, positions, slots, inv_freq, vmix, v_first, q_out, kcache, vcache, q_norm_w, k_norm_w, q_pre_w, k_pre_w)
+    _f32_vec(q_pre_w, heads * dim, op, "q_pre_w")
+    _f32_vec(k_pre_w, kv_heads * dim, op, "k_pre_w")
     _rows_2d(proj, op, "proj")
     _rows_2d(q_out, op, "q_out")
     T = proj.shape[0]
@@ -1370,10 +1509,10 @@ def flex_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, positions:
     if v_mode == 2:
         _f32_vec(vmix, 1, op, "vmix")
     coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
-    f = _fn("attention_flex", "vob_flex_prep", [_P, _I, _L, _I, _I, _I, _P, _P, _P, _I, _I, _F, _F, _I, _P, _P, _P, _P, _I, _P, _L, _P, _P,
-                                                _I, _I, _I, _I, _I, _I, _P])
+    f = _fn("attention_flex", "vob_flex_prep", [_P, _I, _L, _I, _I, _I, _P, _P, _P, _I, _I, _F, _F, _I, _P, _P, _P, _P, _P, _P, _I, _P, _L,
+                                                _P, _P, _I, _I, _I, _I, _I, _I, _P])
     _check(f(_ptr(proj), _code(proj, op), proj.stride(0), q_off, k_off, v_off, _ptr(positions), _ptr(slots), _ptr(inv_freq), int(rot),
-             1 if unit_rms else 0, float(eps), coef, every, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(vmix), _ptr(v_first), int(v_mode),
+             1 if unit_rms else 0, float(eps), coef, every, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(q_pre_w), _ptr(k_pre_w), _ptr(vmix), _ptr(v_first), int(v_mode),
              _ptr(q_out), q_out.stride(0), _ptr(kcache), _ptr(vcache), T, heads, kv_heads, dim, vdim,
              kcache.shape[2] if kcache is not None else 1, _stream()), op)
 
@@ -1382,14 +1521,18 @@ def flex_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, positions:
 def flex_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                    row_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
                    window: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                   out_scale: float = 1.0, chunk: int = 0, softcap: float = 0.0, dist_bias=None) -> None:
+                   out_scale: float = 1.0, chunk: int = 0, softcap: float = 0.0, dist_bias=None, pool: int = 0) -> None:
     """Causal attention of every row of q [T, heads * dim] over its request's pages, keys of `dim` and values of `vdim`
     features: out [T, heads * vdim] (any row stride) = softmax(q . K * scale) V, over the last `window` keys (0: all), the
     denominator also holding exp(sink[head]) if `sink` (float32 [heads]) is given; times sigmoid(gate) ([T, heads * vdim],
     any row stride) and `out_scale`. `chunk` > 0: a query reads only the keys of its own block of `chunk` positions (blocks
     counted from position 0). `softcap` > 0: score <- softcap * tanh(score / softcap). `dist_bias` = (r1, r2), float32 [heads]
-    each: r1 * ln(1 + r2 * distance) is taken off the score."""
+    each: r1 * ln(1 + r2 * distance) is taken off the score. `pool` > 0 (with a window): every block of `pool` positions that
+    ends at or before position - window is seen as one key and one value, the means of the block's cached keys and values, in
+    the same softmax as the window's tokens."""
     op = "flex_attention"
+    if pool < 0 or (pool and (window <= 0 or chunk)):
+        raise ShapeError(op, f"pooled blocks of {pool} go with a window and without blocks of positions")
     r1, r2 = dist_bias if dist_bias is not None else (None, None)
     _cuda(op, q, out, kcache, vcache, block_tables, row_seq, positions, sink, gate, r1, r2)
     _f32_vec(r1, heads, op, "dist_bias[0]")
@@ -1417,11 +1560,11 @@ def flex_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vca
         if gate.shape != (T, heads * vdim) or gate.dtype != q.dtype:
             raise ShapeError(op, f"gate must be {q.dtype} [{T}, {heads * vdim}], got {gate.dtype} {list(gate.shape)}")
     f = _fn("attention_flex", "vob_flex_attention", [_P, _L, _P, _L, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P,
-                                                     _L, _F, _I, _F, _P, _P, _P])
+                                                     _L, _F, _I, _F, _P, _P, _I, _P])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _code(q, op), _ptr(block_tables),
              block_tables.shape[1], _ptr(row_seq), _ptr(positions), T, heads, kv_heads, dim, vdim, kcache.shape[2], int(window),
              float(scale), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale), int(chunk),
-             float(softcap), _ptr(r1), _ptr(r2), _stream()), op)
+             float(softcap), _ptr(r1), _ptr(r2), int(pool), _stream()), op)
 
 
 # ------------------------------------------------------------------------------------ attention

@@ -5,12 +5,12 @@ from .rotary import Rotary, rotary_inv_freq
 from .attention import Attention
 from .swiglu import SwiGLU
 from .embedding import Embedding, LMHead
-from .block import Block, PostNormBlock
+from .block import Block, PostNormBlock, SandwichBlock
 from .layernorm import LayerNorm
 from .mlp import ActMLP
 from .moe import RoutedExperts
 from .streams import PendingWrite, StreamBlock, StreamCoefficients, StreamEmbedding, StreamNorm
-from .recurrent import GatedDelta, GeneralDelta, Retention
+from .recurrent import GatedDelta, GeneralDelta, Retention, StateSpace
 from .flex_attention import SoftmaxAttention
 from .parallel import ParallelMixer
 from .latent_attention import LatentAttention
@@ -19,4 +19,4 @@ __all__ = ["CacheSpec", "PagedTensorSpec", "StateSpec", "LayerCache", "Workspace
            "PositionEncoding", "LayerCall", "ModelSpec", "FoldedState", "RMSNorm", "Rotary", "rotary_inv_freq", "Attention",
            "SwiGLU", "Embedding", "LMHead", "Block", "PendingWrite", "StreamBlock", "StreamCoefficients", "StreamEmbedding",
            "StreamNorm", "GeneralDelta", "Retention", "LatentAttention", "GatedDelta", "SoftmaxAttention", "ParallelMixer", "PostNormBlock", "LayerNorm",
-           "ActMLP", "RoutedExperts"]
+           "ActMLP", "RoutedExperts", "SandwichBlock", "StateSpace"]

@@ -1,5 +1,6 @@
-"""The arrangements of parts in one layer: the pre-norm residual block (`Block`) and the block whose
-residual takes the normed result of each sub-layer (`PostNormBlock`, at the end of the file).
+"""The arrangements of parts in one layer: the pre-norm residual block (`Block`), the block whose
+residual takes the normed result of each sub-layer (`PostNormBlock`) and the block with a norm on both sides of
+each sub-layer (`SandwichBlock`, at the end of the file).
 
     residual += mixer(norm1(residual));  residual += feed_forward(norm2(residual))
 (crates/engine/src/model.rs:302-332). The residual is float32. Each part's output is not added
@@ -17,7 +18,7 @@ from typing import Optional
 
 import torch
 
-from .base import FeedForward, FoldedState, LayerCache, Mixer, Norm, StepContext, aligned
+from .base import FeedForward, FoldedState, LayerCache, Mixer, Norm, StateSpec, StepContext, aligned
 
 
 class Block:
@@ -187,4 +188,121 @@ class PostNormBlock:
                     self.norm2.add_normed(resid, f, out if narrow else None)
         if narrow:
             ctx.shared[self.STREAM_COPY] = out
+        return None
+
+
+class SandwichBlock:
+    """residual += post1(mixer(c1(pre1(residual))));  residual += post2(feed_forward(c2(pre2(residual))))
+
+    A norm in front of each sub-layer and another on its result. Options, each off when its argument is None:
+
+    * `canon1`, `canon2` ([width, taps] each): what a sub-layer reads, h, is first replaced by h + conv(h), a short causal
+      convolution over time on each feature, conv(h)_t = sum_j w[:, j] * h_(t - taps + 1 + j); the last taps - 1 inputs of
+      a request are part of its state (the block answers `state_spec()` for them and for its mixer);
+    * `depth_weights` ([n + 1], with `depth_index` = n - 1 and `depth_slots`): the stream is a learned sum over depth. The
+      block files its result as entry n of `ctx.shared[depth_name]` (float32 [rows, depth_slots * width]; entry 0 is the
+      embedding's output, filed by the block with `depth_index` 0) and hands on sum_j depth_weights[j] * entry j.
+
+    The pre-norms offer `forward(resid, None, ctx)`, the post-norms `add_normed(resid, result, copy)` (`LayerNorm`). A block
+    without feed-forward has neither second norm. Nothing is left pending: the block returns None."""
+
+    def __init__(self, pre1: Norm, mixer: Mixer, post1: Norm, pre2: Optional[Norm], feed_forward: Optional[FeedForward],
+                 post2: Optional[Norm], canon1: Optional[torch.Tensor] = None, canon2: Optional[torch.Tensor] = None,
+                 depth_weights: Optional[torch.Tensor] = None, depth_index: int = 0, depth_slots: int = 0,
+                 depth_name: str = "depth_stack", device="cuda"):
+        self.norm1, self.mixer, self.post1 = pre1, mixer, post1
+        self.norm2, self.feed_forward, self.post2 = pre2, feed_forward, post2
+        if (pre2 is None) != (feed_forward is None) or (post2 is None) != (feed_forward is None):
+            raise ValueError("a block has its second pair of norms exactly when it has a feed-forward")
+        for n in (post1, post2):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ValueError("the norms behind the sub-layers must offer add_normed(resid, result, copy)")
+        if canon2 is not None and feed_forward is None:
+            raise ValueError("a convolution in front of a feed-forward that is not there")
+        f32 = dict(device=device, dtype=torch.float32)
+        self.canon1 = canon1.to(**f32).contiguous() if canon1 is not None else None
+        self.canon2 = canon2.to(**f32).contiguous() if canon2 is not None else None
+        for c in (self.canon1, self.canon2):
+            if c is not None and (c.dim() != 2 or c.shape[1] < 1):
+                raise ValueError(f"a convolution's weights are [width, taps], got {list(c.shape)}")
+        self.depth_weights = depth_weights.to(**f32).contiguous() if depth_weights is not None else None
+        self.depth_index, self.depth_slots, self.depth_name = int(depth_index), int(depth_slots), depth_name
+        if self.depth_weights is not None and (self.depth_weights.shape != (self.depth_index + 2,) or self.depth_slots < self.depth_index + 2):
+            raise ValueError(f"the block at depth {depth_index} takes {self.depth_index + 2} weights and as many entries, got "
+                             f"{list(self.depth_weights.shape)} and {depth_slots}")
+        self.pending_scale = None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.post1, self.norm2, self.feed_forward, self.post2) if p is not None]
+
+    def _own_states(self):
+        return [c for c in (self.canon1, self.canon2) if c is not None and c.shape[1] > 1]
+
+    def state_spec(self):
+        """The convolutions' last inputs (one tensor each, [taps - 1, width]), then the mixer's own state."""
+        own = [StateSpec((c.shape[1] - 1, c.shape[0]), torch.float32) for c in self._own_states()]
+        ms = self.mixer.state_spec()
+        ms = [] if ms is None else list(ms) if isinstance(ms, (tuple, list)) else [ms]
+        return tuple(own + ms) if own or ms else None
+
+    def weight_bytes(self) -> int:
+        own = sum(t.numel() * 4 for t in (self.canon1, self.canon2, self.depth_weights) if t is not None)
+        return own + sum(getattr(p, "weight_bytes", lambda: 0)() for p in self._parts())
+
+    def workspace_bytes(self, rows: int, hidden: int, act_bytes: int) -> int:
+        """The normed input, its convolved form, one sub-layer's result, and the larger of the two sub-layers' own scratch."""
+        ff = self.feed_forward.workspace_bytes(rows) if self.feed_forward is not None else 0
+        return 3 * aligned(rows * hidden * act_bytes) + max(self.mixer.workspace_bytes(rows), ff)
+
+    def folded_workspace_bytes(self, rows: int) -> int:
+        return 0
+
+    def kernel_modules(self, dtype, max_rows):
+        mods = ["elementwise"] + (["recurrence"] if self.canon1 is not None or self.canon2 is not None else [])
+        for p in self._parts():
+            mods += list(getattr(p, "kernel_modules", lambda d, r: ())(dtype, max_rows))
+        return tuple(mods)
+
+    def can_fold(self) -> bool:
+        return False
+
+    def _read(self, norm: Norm, canon, conv_state, resid, ctx: StepContext):
+        """What a sub-layer reads: the normed residual, with its convolution added where there is one."""
+        from .. import kernels
+        h = norm.forward(resid, None, ctx)
+        if canon is None:
+            return h
+        hc = ctx.alloc(h.shape)
+        kernels.causal_conv(h, canon, None, conv_state, ctx.positions, ctx.row_seq, ctx.seq_starts, ctx.state_slots, ctx.seqs, hc,
+                            residual=True)
+        if conv_state is not None:
+            kernels.conv_state_update(h, 0, conv_state, ctx.seq_starts, ctx.state_slots, ctx.seqs)
+        return hc
+
+    def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: Optional[LayerCache], state, out: torch.Tensor, pending_scale: Optional[torch.Tensor] = None):
+        if pending is not None:
+            raise ValueError("a block of this arrangement follows blocks that leave nothing pending")
+        from .. import kernels
+        ws = ctx.workspace
+        states = list(state) if isinstance(state, (tuple, list)) else [] if state is None else [state]
+        own = [states.pop(0) for _ in self._own_states()]
+        cs1 = own.pop(0) if self.canon1 is not None and self.canon1.shape[1] > 1 else None
+        cs2 = own.pop(0) if self.canon2 is not None and self.canon2.shape[1] > 1 else None
+        ms = self.mixer.state_spec()
+        mixer_state = None if ms is None else tuple(states) if isinstance(ms, (tuple, list)) else states[0]
+        stack = None
+        if self.depth_weights is not None:
+            stack = ctx.shared[self.depth_name].view(resid.shape[0], self.depth_slots, resid.shape[1])
+            if self.depth_index == 0:
+                kernels.depth_average(stack, resid, None, 0)
+        with ws.scope():
+            m = self.mixer.forward(self._read(self.norm1, self.canon1, cs1, resid, ctx), ctx, cache, mixer_state)
+            self.post1.add_normed(resid, m, None)
+        if self.feed_forward is not None:
+            with ws.scope():
+                f = self.feed_forward.forward(self._read(self.norm2, self.canon2, cs2, resid, ctx), ctx)
+                self.post2.add_normed(resid, f, None)
+        if stack is not None:
+            kernels.depth_average(stack, resid, self.depth_weights, self.depth_index + 1)
         return None

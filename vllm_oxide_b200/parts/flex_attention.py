@@ -12,6 +12,11 @@ as parameters:
 * `rot_dims`, `rot_base`   partial rotary positions, feature i paired with i + rot_dims / 2;
 * `unit_rms_eps`     q and k divided by sqrt(mean(x^2) + eps) per head, after the rotation;
 * `q_norm_weight`, `k_norm_weight`   [dim] each, shared by the heads: q and k times it behind that division;
+* `q_pre_norm`, `k_pre_norm`   [heads * dim] / [kv_heads * dim], with `pre_norm_eps`: BEFORE the rotation the whole q (k)
+                     projection, all heads at once, is divided by its root mean square and multiplied by that weight;
+* `pool`             (with `window`) beside the window's tokens a query sees one key and value for every block of `pool`
+                     positions that lies wholly before the window: the means of the block's cached keys and values, in the
+                     same softmax (the cache then keeps every token);
 * `chunk`            a query sees only the keys of its own block of `chunk` positions, blocks counted from position 0
                      (pages of earlier blocks are given back);
 * `softcap`          score <- softcap * tanh(score / softcap);
@@ -51,7 +56,9 @@ class SoftmaxAttention(Mixer):
                  sink: Optional[torch.Tensor] = None, gate_weight: Optional[torch.Tensor] = None, value_mix: Optional[str] = None,
                  mix_weight: Optional[torch.Tensor] = None, shared_name: str = "v_first", q_norm_weight: Optional[torch.Tensor] = None,
                  k_norm_weight: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0, dist_bias=None,
-                 shared_kv: bool = False, cache_keep: Optional[Tuple[str, int]] = None, dtype=torch.bfloat16, device="cuda"):
+                 shared_kv: bool = False, cache_keep: Optional[Tuple[str, int]] = None, dtype=torch.bfloat16, device="cuda",
+                 q_pre_norm: Optional[torch.Tensor] = None, k_pre_norm: Optional[torch.Tensor] = None,
+                 pre_norm_eps: Optional[float] = None, pool: int = 0):
         self.H, self.G, self.D, self.DV = int(heads), int(kv_heads), int(dim), int(vdim)
         self.shared_kv = bool(shared_kv)
         if self.shared_kv:
@@ -101,7 +108,10 @@ class SoftmaxAttention(Mixer):
         self.softcap = float(softcap) if softcap else 0.0
         if self.softcap < 0:
             raise ValueError(f"softcap {softcap} must be positive")
-        own = ("window", self.window) if self.window else ("chunk", self.chunk) if self.chunk else ("full", 0)
+        self.pool = int(pool) if pool else 0
+        if self.pool < 0 or (self.pool and not self.window):
+            raise ValueError(f"pooled blocks of {pool} go with a window")
+        own = ("full", 0) if self.pool else ("window", self.window) if self.window else ("chunk", self.chunk) if self.chunk else ("full", 0)
         self.cache_keep = (str(cache_keep[0]), int(cache_keep[1])) if cache_keep is not None else own
         if self.cache_keep != own and self.cache_keep[0] != "full":
             raise ValueError(f"a cache that keeps {self.cache_keep} cannot serve a layer that reads {own}")
@@ -119,6 +129,14 @@ class SoftmaxAttention(Mixer):
                 raise ValueError(f"{name} must have {self.D} entries and goes with unit_rms_eps, got {list(nw.shape)}")
         self.q_norm_w = q_norm_weight.to(**f32).contiguous() if q_norm_weight is not None else None
         self.k_norm_w = k_norm_weight.to(**f32).contiguous() if k_norm_weight is not None else None
+        if (q_pre_norm is not None and q_pre_norm.shape != (nq,)) or (k_pre_norm is not None and (self.shared_kv or k_pre_norm.shape != (nk,))):
+            raise ValueError(f"the norms over the whole projections take {nq} and {nk} weights (none for keys a layer does not make)")
+        if (q_pre_norm is not None or k_pre_norm is not None) and (pre_norm_eps is None or self.unit_rms):
+            raise ValueError("a norm over the whole projection needs its eps and does not go with the norm per head")
+        self.q_pre_w = q_pre_norm.to(**f32).contiguous() if q_pre_norm is not None else None
+        self.k_pre_w = k_pre_norm.to(**f32).contiguous() if k_pre_norm is not None else None
+        if pre_norm_eps is not None and not self.unit_rms:
+            self.eps = float(pre_norm_eps)
         self.dist_bias = None
         if dist_bias is not None:
             r1, r2 = dist_bias
@@ -163,7 +181,7 @@ class SoftmaxAttention(Mixer):
     def plain_scores(self) -> bool:
         """Scores that are q . k * scale and nothing else, over all earlier keys or a window: what the framework's
         tensor-core attention kernels compute."""
-        return not (self.chunk or self.softcap or self.dist_bias is not None)
+        return not (self.chunk or self.softcap or self.dist_bias is not None or self.pool)
 
     def tensor_core_sizes(self) -> bool:
         """Keys and values of one size that the framework's tensor-core attention kernels are built for."""
@@ -208,7 +226,7 @@ class SoftmaxAttention(Mixer):
         kernels.flex_prep(proj, self.q_off, self.k_off, self.v_off, ctx.positions, ctx.slot_mapping[cache.group] if cache.write else None,
                           self.inv_freq, self.rot, self.unit_rms, self.eps, self.q_temp, self.mix_weight, v_first, self.v_mode, q,
                           None if self.shared_kv else kc, None if self.shared_kv else vc, self.H, self.G, self.D, self.DV,
-                          self.q_norm_w, self.k_norm_w)
+                          self.q_norm_w, self.k_norm_w, self.q_pre_w, self.k_pre_w)
         gate = proj[:, self.g_off:self.g_off + self.n_pre] if self.gated else None
         self.attend(q, pre_out, ctx, cache, gate, out_scale)
 
@@ -244,6 +262,10 @@ class SoftmaxAttention(Mixer):
                                              ctx.max_new, H, G, D, self.scale, self.window, self.sink, gate, out_scale)
                 return
         shaped = not self.plain_scores()
+        if self.pool:       # pooled blocks: the general kernel
+            kernels.flex_attention(q, out, kc, vc, bt, ctx.row_seq, ctx.positions, H, G, D, self.DV, self.scale, self.window, self.sink,
+                                   gate, out_scale, self.chunk, self.softcap, self.dist_bias, self.pool)
+            return
         if (self.dtype == torch.bfloat16 and self.impl != "general" and shaped and ctx.decode_only and self.shaped_decode_sizes()
                 and kernels.attn_mma_supported(H, G, D, page, True) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
             self._attend_single(q, out, ctx, cache, bt, ctx.rows, gate, out_scale)

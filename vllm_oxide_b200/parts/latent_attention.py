@@ -12,6 +12,11 @@ works on c directly and returns sum_j p_j c_j, and W_uv,n is applied to that (so
 sum to one, so W_uv (sum_j p_j c_j) = sum_j p_j W_uv c_j). A cached token costs kv_rank + rot_dim
 elements whatever the number of heads, and a decode step reads each of them once for all heads.
 Scores, softmax and the rotation are float32; the query in the latent space stays float32.
+
+Options: `window` (a query sees itself and the window - 1 tokens before it; pages behind the window are given back) and
+`pairing` of the rotated features: "half" (feature i with i + rot_dim / 2) or "interleaved" (2i with 2i + 1). The kernels
+rotate halves; the interleaved pairing is the same rotation on another order of the rotated rows of W_q and W_dkv, the same
+order for both (a score is a dot product, so a common order of q's and k's features changes nothing), applied here at load.
 """
 from __future__ import annotations
 
@@ -27,7 +32,7 @@ from .rotary import rotary_inv_freq
 
 class LatentAttention(Mixer):
     def __init__(self, wq, wdkv, dkv_norm, wuk, wuv, wo, heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
-                 rot_base: float, eps: float, dtype=torch.bfloat16, device="cuda"):
+                 rot_base: float, eps: float, dtype=torch.bfloat16, device="cuda", window: int = 0, pairing: str = "half"):
         self.H, self.D, self.R, self.V, self.L = int(heads), int(dim), int(rot_dim), int(vdim), int(kv_rank)
         H, D, R, V, L = self.H, self.D, self.R, self.V, self.L
         hidden = wq.shape[1]
@@ -36,6 +41,17 @@ class LatentAttention(Mixer):
             raise ValueError(f"projection shapes do not fit {H} heads of {D}+{R} / {V} with a latent of {L} over a width of {hidden}")
         if R % 2 or R <= 0:
             raise ValueError(f"the rotated part must have an even, positive size, got {R}")
+        self.window = int(window) if window else 0
+        if self.window < 0 or pairing not in ("half", "interleaved"):
+            raise ValueError(f"window {window} must not be negative and pairing {pairing!r} is half or interleaved")
+        if pairing == "interleaved":
+            # rotated features in the order 0, 2, 4, ..., 1, 3, 5, ...: pairs (2i, 2i + 1) become (i, i + R / 2)
+            order = torch.cat([torch.arange(0, R, 2), torch.arange(1, R, 2)])
+            qrows = torch.arange(H * (D + R)).view(H, D + R).clone()
+            qrows[:, D:] = qrows[:, D:][:, order]
+            wq = wq[qrows.reshape(-1).to(wq.device)]
+            krows = torch.cat([torch.arange(L), L + order])
+            wdkv = wdkv[krows.to(wdkv.device)]
         self.w_in = to_compute(torch.cat([wq, wdkv], dim=0), dtype, device)
         # per head, as `linear` wants its weights ([out, in]): latent <- plain query features, values <- latent
         self.w_qlat = to_compute(wuk.reshape(H, D, L).transpose(1, 2), dtype, device)          # [H, L, D]
@@ -59,7 +75,8 @@ class LatentAttention(Mixer):
         return max(1, min(32, 2 * self.num_sms // blocks)) if blocks < self.num_sms else 1
 
     def cache_spec(self) -> Optional[CacheSpec]:
-        return CacheSpec(kind="full", tensors=(PagedTensorSpec(1, self.L), PagedTensorSpec(1, self.R)))
+        kind = "window" if self.window else "full"
+        return CacheSpec(kind=kind, window=self.window, tensors=(PagedTensorSpec(1, self.L), PagedTensorSpec(1, self.R)))
 
     def weight_bytes(self) -> int:
         return (self.w_in.numel() + self.w_qlat.numel() + self.w_val.numel() + self.w_o.numel()) * self.w_in.element_size()
@@ -100,10 +117,10 @@ class LatentAttention(Mixer):
             if self.tensor_cores and self._tc_ok and not ctx.decode_only and ctx.max_new > 1:
                 # prompt portions: scores and the weighted sum on the tensor cores, 16 tokens of a request at a time
                 kernels.latent_attend_tc(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.seq_starts, ctx.positions, ctx.seqs,
-                                         min(ctx.max_new, T), self.scale, out_lat.transpose(0, 1))
+                                         min(ctx.max_new, T), self.scale, out_lat.transpose(0, 1), self.window)
             else:
                 kernels.latent_attend(q_lat.transpose(0, 1), q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale,
-                                      out_lat.transpose(0, 1), splits, partials)
+                                      out_lat.transpose(0, 1), splits, partials, self.window)
             vals = ctx.alloc((H, T, V))
             torch.bmm(out_lat, self.w_val.transpose(1, 2), out=vals)
             attn = ctx.alloc((T, H * V))
@@ -113,7 +130,7 @@ class LatentAttention(Mixer):
             for h in range(H):
                 kernels.linear(q_heads[:, h], self.w_qlat[h], q_lat[:, h])
             out_lat = ctx.alloc((T, H, L))
-            kernels.latent_attend(q_lat, q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat, splits, partials)
+            kernels.latent_attend(q_lat, q_rot, lat, kr, bt, ctx.row_seq, ctx.positions, self.scale, out_lat, splits, partials, self.window)
             attn = ctx.alloc((T, H * V))
             for h in range(H):
                 kernels.linear(out_lat[:, h], self.w_val[h], attn[:, h * V:(h + 1) * V])

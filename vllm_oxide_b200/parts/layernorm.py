@@ -1,4 +1,4 @@
-"""Layer norm with weight and bias: LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * w + b, sums in float32.
+"""Layer norm with weight and (optionally) bias: LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * w + b, sums in float32.
 
 Two uses. As any norm of this engine it normalises the float32 residual (after adding what is still
 pending) for the part that follows: `forward`. In a block whose residual takes the NORMED result of each
@@ -18,16 +18,17 @@ from .base import Norm, StepContext, aligned
 class LayerNorm(Norm):
     scale_and_weight = False      # the mean and the bias do not commute with a matrix product: no folded form
 
-    def __init__(self, weight: torch.Tensor, bias: torch.Tensor, eps: float, device):
-        if weight.dim() != 1 or bias.shape != weight.shape:
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, device):
+        """`bias` None: a layer norm with a weight only."""
+        if weight.dim() != 1 or (bias is not None and bias.shape != weight.shape):
             raise ValueError(f"layer norm needs a weight and a bias of one length, got {list(weight.shape)} and {list(bias.shape)}")
         self.weight = weight.to(device=device, dtype=torch.float32).contiguous()
-        self.bias = bias.to(device=device, dtype=torch.float32).contiguous()
+        self.bias = bias.to(device=device, dtype=torch.float32).contiguous() if bias is not None else None
         self.eps = float(eps)
         self.width = weight.shape[0]
 
     def weight_bytes(self) -> int:
-        return 2 * self.weight.numel() * 4
+        return (2 if self.bias is not None else 1) * self.weight.numel() * 4
 
     def workspace_bytes(self, rows: int, act_bytes: int) -> int:
         return aligned(rows * self.width * act_bytes)

@@ -5,6 +5,11 @@
     runs can be chosen (no groups: all can);  the `top` experts with the largest s are chosen
     out = sum over the chosen e of w_e * W_down[e] (silu(W_gate[e] x) * (W_up[e] x)),   w_e = s_e (or s_e / their sum)
 
+Options: `activation` "clamped_swish" with `limit` (g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) *
+(u + 1) in place of silu(gate) * up); `shared` = (w_gate, w_up, w_down, w_gate_scalar or None, limit): one more expert of the
+same form that every token uses, added to the sum, times sigmoid(w_gate_scalar x) (one number per token) where that is given.
+Softmax over all experts followed by `renormalize` over the chosen ones is the softmax over the chosen logits alone.
+
 Per step: the election (one warp per token), the (token, expert) pairs put in order of their expert on the device
 (no count ever goes to the host, so the step can be recorded in a CUDA graph), one grouped product for gate and up
 with the gate in its epilogue, one for down with the weight in its epilogue, and the sum over a token's choices in
@@ -26,7 +31,7 @@ from .linear import to_compute
 class RoutedExperts(FeedForward):
     def __init__(self, w_router: torch.Tensor, w_gate: Sequence[torch.Tensor], w_up: Sequence[torch.Tensor],
                  w_down: Sequence[torch.Tensor], top: int, groups: int = 0, keep: int = 0, renormalize: bool = False,
-                 dtype=torch.bfloat16, device="cuda"):
+                 dtype=torch.bfloat16, device="cuda", activation: str = "silu", limit: float = 0.0, shared=None):
         E, hidden = w_router.shape
         if not (len(w_gate) == len(w_up) == len(w_down) == E):
             raise ValueError(f"the router names {E} experts, got {len(w_gate)} / {len(w_up)} / {len(w_down)} sets of weights")
@@ -49,21 +54,43 @@ class RoutedExperts(FeedForward):
         self.dtype = dtype
         self.tensor_cores = dtype == torch.bfloat16
         self.meta = torch.zeros(4, dtype=torch.int32, device=device)
+        if activation not in kernels.MOE_ACTIVATIONS or (activation == "clamped_swish" and not limit > 0):
+            raise ValueError(f"activation {activation!r} with limit {limit}: known are {', '.join(kernels.MOE_ACTIVATIONS)}, and the "
+                             f"clamped one needs a positive limit")
+        self.activation, self.limit = activation, float(limit)
+        self.shared = None
+        if shared is not None:
+            sg, su, sd, sgate, slimit = shared
+            fs = sg.shape[0]
+            if sg.shape != (fs, hidden) or su.shape != (fs, hidden) or sd.shape != (hidden, fs) or (sgate is not None and sgate.shape != (1, hidden)):
+                raise ValueError(f"the shared expert's shapes {list(sg.shape)} / {list(su.shape)} / {list(sd.shape)} do not fit a width of {hidden}")
+            # [gate; up; the gate's one row; zero rows up to a multiple of 8]: one product gives all of them
+            rows = [sg, su] + ([sgate, torch.zeros((7, hidden), dtype=sg.dtype, device=sg.device)] if sgate is not None else [])
+            self.shared = (to_compute(torch.cat([r.to(sg.device) for r in rows], dim=0), dtype, device), to_compute(sd, dtype, device), fs,
+                           sgate is not None, float(slimit))
+            if activation == "clamped_swish" and not slimit > 0:
+                raise ValueError("the shared expert's limit must be positive")
 
     def weight_bytes(self) -> int:
         """What a step of one token reads: the router and `top` experts."""
         es = self.w_down.element_size()
-        return self.w_router.numel() * 4 + self.top * 3 * self.ff * self.hidden * es
+        shared = (self.shared[0].numel() + self.shared[1].numel()) * es if self.shared is not None else 0
+        return self.w_router.numel() * 4 + self.top * 3 * self.ff * self.hidden * es + shared
 
     def workspace_bytes(self, rows: int) -> int:
         es = 2 if self.dtype == torch.bfloat16 else 4
         P = rows * self.top
         cap = max(kernels.moe_sorted_rows(P, self.E, r) for r in (kernels.MOE_TILE_ROWS, kernels.MOE_LARGE_TILE_ROWS))
-        return (2 * aligned(P * 4) + aligned(cap * 4) + aligned(cap // kernels.MOE_TILE_ROWS * 4) + aligned(P * self.ff * es)
+        shared = 0
+        if self.shared is not None:
+            shared = aligned(rows * self.shared[0].shape[0] * es) + aligned(rows * self.shared[2] * es) + aligned(rows * self.hidden * es)
+        return shared + (2 * aligned(P * 4) + aligned(cap * 4) + aligned(cap // kernels.MOE_TILE_ROWS * 4) + aligned(P * self.ff * es)
                 + aligned(P * self.hidden * 4) + aligned(rows * self.hidden * es))
 
     def kernel_modules(self, dtype, max_rows):
-        return ("moe",)
+        if self.shared is None:
+            return ("moe",)
+        return ("moe", "elementwise") + (("gemm_f32",) if dtype == torch.float32 else ("gemm_sm100",))
 
     def forward(self, x: torch.Tensor, ctx: StepContext, out=None) -> torch.Tensor:
         T = x.shape[0]
@@ -76,9 +103,22 @@ class RoutedExperts(FeedForward):
         order, tile_expert = ctx.alloc((cap,), torch.int32), ctx.alloc((cap // tile,), torch.int32)
         kernels.moe_align(idx, self.E, order, tile_expert, self.meta, tile)
         h = ctx.alloc((P, self.ff))
-        kernels.moe_gate_up(x, self.w_gu, order, tile_expert, self.top, h, self.tensor_cores, tile)
+        kernels.moe_gate_up(x, self.w_gu, order, tile_expert, self.top, h, self.tensor_cores, tile, self.activation, self.limit)
         y = ctx.alloc((P, self.hidden), torch.float32)
         kernels.moe_down(h, self.w_down, order, tile_expert, w, y, self.tensor_cores, tile)
         out = out if out is not None else ctx.alloc((T, self.hidden))
-        kernels.moe_combine(y, idx, out)
+        sh = sgate = None
+        if self.shared is not None:
+            w_gu, w_down, fs, gated, slimit = self.shared
+            gu = ctx.alloc((T, w_gu.shape[0]))
+            kernels.linear(x, w_gu, gu)
+            hs = ctx.alloc((T, fs))
+            if self.activation == "clamped_swish":
+                kernels.glu_clamped(gu[:, :2 * fs], hs, slimit)
+            else:
+                kernels.glu(gu[:, :2 * fs], hs, "silu")
+            sh = ctx.alloc((T, self.hidden))
+            kernels.linear(hs, w_down, sh)
+            sgate = gu[:, 2 * fs] if gated else None
+        kernels.moe_combine(y, idx, out, sh, sgate)
         return out

@@ -24,6 +24,13 @@ may share one q and k head):
   second matrix), and an output gate from one full projection, silu(W_g h) or sigmoid(W_g h).
 Its state is the matrix S and, in a second tensor, the convolutions' last taps - 1 inputs.
 
+`StateSpace`, a selective state-space mixer (the state-space duality form), per head of `vdim` values with a state of
+`state` key channels, the heads in `groups` that share B and C:
+    [z | x | B | C | dt] = W_in h;   x, B, C = silu(conv([x | B | C]) + conv_bias)    one short causal convolution per channel
+    dt = softplus(dt + dt_bias);   S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T;   y_t = S_t^T C_t + D_h x_t
+    out = W_o (rms_groups(y * silu(z)) * norm_weight)      the gate first, then an RMS norm over `norm_groups` equal parts
+Its state is the matrix S [state, vdim] per head and the convolution's last taps - 1 inputs.
+
 All run the same scan kernel (`kernels.recurrence_scan`) for prompt portions and single tokens
 alike. The projections are one matrix product each side of it, in the compute dtype; everything
 between them that enters the recurrence (unit key, decay, removal rate, rotation, the state, the
@@ -261,3 +268,75 @@ class GatedDelta(Mixer):
         pre = ctx.alloc((T, self.n_pre))
         self.core(proj, ctx, cache, state, pre)
         return matmul(pre, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
+
+
+class StateSpace(Mixer):
+    """See the module's head. `w_in` [2 * heads * vdim + 2 * groups * state + heads, width] in the order z, x, B, C, dt;
+    `conv_w` [heads * vdim + 2 * groups * state, taps] (last column the current token's) with `conv_b`; `dt_bias`, `a_log`,
+    `d_skip` [heads]; `norm_weight` [heads * vdim]."""
+
+    def __init__(self, w_in, conv_w, conv_b, dt_bias, a_log, d_skip, norm_weight, wo, heads: int, vdim: int, state: int, groups: int,
+                 norm_groups: int, eps: float, dtype=torch.bfloat16, device="cuda"):
+        self.H, self.P, self.N, self.G, self.NG = int(heads), int(vdim), int(state), int(groups), int(norm_groups)
+        H, P, N, G = self.H, self.P, self.N, self.G
+        if G <= 0 or H % G:
+            raise ValueError(f"{H} heads are not a multiple of {G} groups")
+        if N > 512:
+            raise ValueError(f"a state of {N} channels is beyond the scan's 512")
+        self.inner, self.GN = H * P, G * N
+        if self.NG <= 0 or self.inner % self.NG:
+            raise ValueError(f"{self.inner} features do not split into {self.NG} norm groups")
+        self.C = self.inner + 2 * self.GN
+        hidden = w_in.shape[1]
+        rows = 2 * self.inner + 2 * self.GN + H
+        if w_in.shape != (rows, hidden) or wo.shape != (hidden, self.inner):
+            raise ValueError(f"projections {list(w_in.shape)} / {list(wo.shape)} do not fit {H} heads of {P} with a state of {N} in {G} "
+                             f"groups over a width of {hidden}")
+        if conv_w.dim() != 2 or conv_w.shape[0] != self.C or conv_b.shape != (self.C,):
+            raise ValueError(f"the convolution takes [{self.C}, taps] weights and [{self.C}] biases, got {list(conv_w.shape)} / {list(conv_b.shape)}")
+        self.taps = conv_w.shape[1]
+        for name, t, n in (("dt_bias", dt_bias, H), ("A_log", a_log, H), ("D", d_skip, H), ("norm", norm_weight, self.inner)):
+            if t.shape != (n,):
+                raise ValueError(f"'{name}' must have {n} entries, got {list(t.shape)}")
+        self.w_in = to_compute(w_in, dtype, device)
+        self.w_o = to_compute(wo, dtype, device)
+        f32 = dict(device=device, dtype=torch.float32)
+        self.conv_w, self.conv_b = conv_w.to(**f32).contiguous(), conv_b.to(**f32).contiguous()
+        self.dt_bias, self.a_log, self.d_skip = dt_bias.to(**f32).contiguous(), a_log.to(**f32).contiguous(), d_skip.to(**f32).contiguous()
+        self.norm_weight = norm_weight.to(**f32).contiguous()
+        self.eps, self.hidden, self.dtype = float(eps), hidden, dtype
+
+    def state_spec(self):
+        s = StateSpec((self.H, self.N, self.P), torch.float32)
+        return (s, StateSpec((self.taps - 1, self.C), torch.float32)) if self.taps > 1 else (s,)
+
+    def weight_bytes(self) -> int:
+        return (self.w_in.numel() + self.w_o.numel()) * self.w_in.element_size() + (self.conv_w.numel() + self.conv_b.numel()) * 4
+
+    def workspace_bytes(self, rows: int) -> int:
+        es = self.w_in.element_size()
+        return (aligned(rows * self.w_in.shape[0] * es) + aligned(rows * self.C * 4) + 2 * aligned(rows * self.H * 4)
+                + aligned(rows * self.inner * 4) + aligned(rows * self.inner * es) + aligned(rows * self.hidden * es))
+
+    def kernel_modules(self, dtype, max_rows):
+        return _modules(dtype)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache], state, out=None) -> torch.Tensor:
+        if state is None:
+            raise ValueError("the state-space mixer needs its state")
+        S, conv_state = state[0], (state[1] if self.taps > 1 else None)
+        T, inner, GN, C, H = x.shape[0], self.inner, self.GN, self.C, self.H
+        proj = matmul(x, self.w_in, ctx.alloc((T, self.w_in.shape[0])))
+        xbc = ctx.alloc((T, C), torch.float32)
+        kernels.causal_conv(proj[:, inner:inner + C], self.conv_w, self.conv_b, conv_state, ctx.positions, ctx.row_seq, ctx.seq_starts,
+                            ctx.state_slots, ctx.seqs, xbc, residual=False, act="silu")
+        if conv_state is not None:
+            kernels.conv_state_update(proj, inner, conv_state, ctx.seq_starts, ctx.state_slots, ctx.seqs)
+        dt, decay = ctx.alloc((T, H), torch.float32), ctx.alloc((T, H), torch.float32)
+        kernels.ssm_steps(proj[:, inner + C:inner + C + H], self.dt_bias, self.a_log, dt, decay)
+        o = ctx.alloc((T, inner), torch.float32)
+        kernels.recurrence_scan(3, xbc[:, inner + GN:], xbc[:, inner:inner + GN], xbc[:, :inner], None, decay, dt, S, ctx.seq_starts,
+                                ctx.state_slots, ctx.seqs, H, o, rk_heads=self.G)
+        y = ctx.alloc((T, inner))
+        kernels.ssm_post(o, xbc[:, :inner], proj[:, :inner], self.d_skip, self.norm_weight, self.eps, H, self.NG, y)
+        return matmul(y, self.w_o, out if out is not None else ctx.alloc((T, self.hidden)))
