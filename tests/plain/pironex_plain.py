@@ -84,13 +84,14 @@ def attention_keys_values(h, t, p, m, eps):
     return k, v
 
 
-def pooled_window_attention(q, k, v, scale, softcap, size, pool):
+def pooled_window_attention(q, k, v, scale, softcap, size, pool, rows=None):
     """q [T, H, d], k [T, G, d], v [T, G, dv] -> [T, H, dv]. Row i sees the tokens j with 0 <= i - j < size and, for each
-    block b of `pool` tokens that ends at or before i - size, the mean of the block's keys with the mean of its values."""
+    block b of `pool` tokens that ends at or before i - size, the mean of the block's keys with the mean of its values.
+    `rows`: only these rows are worked out (the others stay zero)."""
     T, H, _ = q.shape
     G = k.shape[1]
     out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
-    for i in range(T):
+    for i in (range(T) if rows is None else rows):
         lo = max(0, i - size + 1) if size else 0
         ks, vs = [k[j] for j in range(lo, i + 1)], [v[j] for j in range(lo, i + 1)]
         if size and pool:
@@ -129,7 +130,7 @@ def mamba2_mixer(h, t, p, m, eps):
     H, P, N, G = m["heads"], m["vdim"], m["state"], m["groups"]
     inner = H * P
     proj = h @ t[p + "in"].T
-    z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N], proj[:, 2 * inner + 2 * G * N:]
+    z, xbc, dt = proj[:, :inner], proj[:, inner:2 * inner + 2 * G * N].clone(), proj[:, 2 * inner + 2 * G * N:]
     xbc = silu(causal_conv(xbc, t[p + "conv"], t[p + "conv.b"]))
     x = xbc[:, :inner].reshape(T, H, P)
     B = xbc[:, inner:inner + G * N].reshape(T, G, N)
@@ -197,16 +198,21 @@ def moe(h, t, p, m):
 
 
 # ----------------------------------------------------------------------------------- the model
-def forward(cfg: dict, t: dict, tokens, layers_out=None):
-    """tokens: list of ints -> logits [T, vocab]. `layers_out` (a list) receives every layer's result."""
+def forward(cfg: dict, t: dict, tokens, dtype=None, layers_out=None):
+    """tokens: list of ints -> logits [T, vocab]. `layers_out` (a list) receives the stream that every layer hands on."""
+    if dtype is not None:
+        t = {k: v.to(dtype) if v.is_floating_point() else v for k, v in t.items()}
     eps = cfg["norm"]["eps"]
-    x = t["embed"][torch.tensor(tokens)] * cfg["embedding"]["scale"]
+    x = t["embed"][torch.tensor(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     results = [x]
     kvs = {}
     for i, layer in enumerate(cfg["layers"]):
         pre = f"l{i}."
         m = layer["mixer"]
-        h = canon(layer_norm(x, t[pre + "norm1"], eps), t[pre + "canon1"])
+        has_canon = cfg.get("canon") is not None
+        h = layer_norm(x, t[pre + "norm1"], eps)
+        if has_canon:
+            h = canon(h, t[pre + "canon1"])
         if layer["type"] == "attention":
             src = m.get("kv_from")
             if src is None:
@@ -218,11 +224,13 @@ def forward(cfg: dict, t: dict, tokens, layers_out=None):
             y = latent_mixer(h, t, pre + "mix.", m, eps)
         x = x + layer_norm(y, t[pre + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            h = canon(layer_norm(x, t[pre + "norm2"], eps), t[pre + "canon2"])
+            h = layer_norm(x, t[pre + "norm2"], eps)
+            if has_canon:
+                h = canon(h, t[pre + "canon2"])
             x = x + layer_norm(moe(h, t, pre + "mlp.", layer["mlp"]), t[pre + "norm2b"], eps)
         results.append(x)
-        if layers_out is not None:
-            layers_out.append(x)
         w = t[pre + "dwa"]
         x = sum(w[j] * results[j] for j in range(i + 2))
+        if layers_out is not None:
+            layers_out.append(x)
     return layer_norm(x, t["final.norm"], eps) @ t["embed"].T
