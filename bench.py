@@ -1062,6 +1062,154 @@ def bufulorn_compare(a):
     return 0
 
 
+# Layer sizes at which the Pironex design is measured beside Bufulorn, the closest design the engine has (attention with a cap
+# that may read another layer's keys and values, a recurrent mixer with short convolutions, routed experts, layer norms on the
+# sub-layers' results), at the same width, attention heads and recurrent sizes (those of LOMOPEL_SIZES): the window and the
+# pooled blocks, the latent attention (the sizes of ROTEPEL_SIZES), the state-space mixer and the experts.
+PIRONEX_SIZES = {
+    "1b": dict(bufulorn="1b", window=1024, pool=64, softcap=30.0, taps=4, moe=dict(ff=1024, limit=7.0, experts=8, top=2, shared_ff=2048, shared_limit=7.0)),
+    "3b": dict(bufulorn="3b", window=1024, pool=64, softcap=30.0, taps=4, moe=dict(ff=1024, limit=7.0, experts=8, top=2, shared_ff=2048, shared_limit=7.0)),
+}
+
+
+def pironex_parts(ps):
+    ls = LOMOPEL_SIZES[BUFULORN_SIZES[ps["bufulorn"]]["lomopel"]]
+    d, lat = ls["delta"], ROTEPEL_SIZES[ls["llama"]]["latent"]
+    ssm = dict(heads=d["heads"], vdim=d["vdim"], state=d["dim"], groups=d["kv_heads"], norm_groups=d["kv_heads"], conv=d["conv"])
+    return ls, ssm, lat
+
+
+def make_pironex_engine(ps, blocks, max_seqs, tokens_per_request, context):
+    """(config, LLM): `blocks` times the four layers [state space, latent attention in a window, attention with a window and
+    pooled blocks, attention that reads that layer's keys and values], each with routed experts and a shared expert, random
+    weights drawn on the device."""
+    import torch
+    from vllm_oxide_b200 import models
+    from vllm_oxide_b200.config import (ClampedExpertsConfig, EngineConfig, PironexConfig, PironexLayer, PooledAttentionConfig,
+                                        StateSpaceConfig, WindowLatentConfig)
+    from vllm_oxide_b200.engine import LLM, ModelRunner
+    from vllm_oxide_b200.weights import random_tensors
+    ls, ssm, lat = pironex_parts(ps)
+    at = ls["attn"]
+    moe = ClampedExpertsConfig(**ps["moe"])
+    layers = []
+    for b in range(blocks):
+        common = dict(scale=at["dim"] ** -0.5, softcap=ps["softcap"], rot_dims=at["dim"] // 2, rot_base=5e5, window=ps["window"], pool=ps["pool"], **at)
+        layers += [PironexLayer("mamba2", ssm=StateSpaceConfig(**ssm), mlp=moe),
+                   PironexLayer("latent_attention", latent=WindowLatentConfig(scale=(lat["dim"] + lat["rot_dim"]) ** -0.5, rot_base=1e4,
+                                                                              window=ps["window"], **lat), mlp=moe),
+                   PironexLayer("attention", attention=PooledAttentionConfig(**common), mlp=moe),
+                   PironexLayer("attention", attention=PooledAttentionConfig(kv_from=4 * b + 2, **common), mlp=moe)]
+    cfg = PironexConfig(vocab=128256, width=ls["width"], norm_eps=1e-5, embedding_scale=1.0, canon_taps=ps["taps"], layers=tuple(layers))
+    pages_per_req = -(-(tokens_per_request + 16) // 16)
+    fields = dict(max_batch_tokens=2048, max_seqs=max_seqs, max_model_len=context, block_size=16,
+                  num_pages=max_seqs * pages_per_req + 8, dtype="bfloat16", cuda_graphs=True)
+    fields.update(ENGINE_OVERRIDES)
+    tensors = random_tensors(models.pironex_manifest(cfg), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0")
+    runner = ModelRunner(cfg, tensors, EngineConfig(**fields))
+    del tensors
+    return cfg, LLM(runner)
+
+
+def pironex_roofline(ps, blocks, n, batch, peaks, prefill, decode):
+    """The design's own kernels against their rooflines: algorithmic bytes (or FLOPs) of all their launches in one step
+    over the measured time, as a fraction of the measured copy bandwidth (or the measured bfloat16 product rate)."""
+    ls, ssm, lat = pironex_parts(ps)
+    at, W, win, pool, m, taps = ls["attn"], ls["width"], ps["window"], ps["pool"], ps["moe"], ps["taps"]
+    layers = 4 * blocks
+    out = {}
+
+    def add(names, label, phase, totals, nbytes=None, flops=None):
+        ms = sum(t for op, _, t in totals if op in names)
+        if ms <= 0:
+            return
+        e = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / ms / 1e6, 1)
+            e["of_measured_hbm"] = round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 2)
+            e["of_measured_bf16"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)
+        out[f"{phase}:{label}"] = e
+    qd, kd, vd = at["heads"] * at["dim"], at["kv_heads"] * at["dim"], at["kv_heads"] * at["vdim"]
+    H, P, N, G = ssm["heads"], ssm["vdim"], ssm["state"], ssm["groups"]
+    inner, chans = H * P, H * P + 2 * G * N
+    for phase, rows, totals in (("prefill", n, prefill), ("decode", batch, decode)):
+        # in front of a sub-layer: the float32 residual read, its normed rounding written; behind it: the result read, the
+        # residual read and written
+        add(("layernorm_rows", "layernorm_add"), "layer norms", phase, totals, nbytes=2 * layers * rows * W * ((4 + 2) + (2 + 2 * 4)))
+        # the convolutions in front of the sub-layers (read, written, the state moved on) and the state-space mixer's own
+        add(("causal_conv", "conv_state_update"), "causal convolutions", phase, totals,
+            nbytes=2 * layers * rows * W * (2 + 2) + blocks * rows * chans * (2 + 4))
+        add(("depth_average",), "depth average", phase, totals, nbytes=sum(rows * W * 4 * (i + 4) for i in range(layers)))
+        # keys a row scores: its window's tokens and every token of the pooled blocks behind it (each block is read whole)
+        if phase == "prefill":
+            keys = sum(min(i + 1, win) + max(0, (i - win + 1) // pool) * pool for i in range(n))
+        else:
+            keys = batch * (min(n + 3, win) + max(0, (n + 3 - win) // pool) * pool)
+        add(("flex_attention", "attn_prefill_mma_any", "attn_prefill_mma", "attn_decode_mma"), "attention", phase, totals,
+            nbytes=2 * blocks * keys * (kd + vd) * 2 if phase == "decode" else None, flops=2 * blocks * keys * at["heads"] * 2 * (at["dim"] + at["vdim"]))
+        add(("flex_prep",), "flex_prep", phase, totals, nbytes=blocks * rows * ((2 * qd + 2 * kd + 2 * vd) + 2 * qd) * 2)
+        lkeys = sum(min(i + 1, win) for i in range(n)) if phase == "prefill" else batch * min(n + 3, win)
+        add(("latent_attend", "latent_attend_tc"), "latent attention", phase, totals,
+            nbytes=blocks * lkeys * (lat["kv_rank"] + lat["rot_dim"]) * 2 if phase == "decode" else None,
+            flops=blocks * lkeys * lat["heads"] * 2 * (2 * lat["kv_rank"] + lat["rot_dim"]))
+        seqs = 1 if phase == "prefill" else batch
+        add(("recurrence_scan",), "recurrence_scan", phase, totals,
+            nbytes=blocks * (H * N * P * 4 * 2 * seqs + rows * (2 * G * N * 4 + H * P * 4 + 2 * H * 4 + H * P * 4)), flops=blocks * rows * 2 * H * N * P * 2)
+        add(("ssm_steps", "ssm_post"), "state-space steps, gate and norm", phase, totals,
+            nbytes=blocks * rows * (H * (2 + 8) + inner * (4 + 4 + 2 + 2)))
+        Pn, used = rows * m["top"], min(m["experts"], rows * m["top"])
+        add(("moe_gate_up", "moe_down"), "expert products", phase, totals,
+            nbytes=layers * (used * 3 * m["ff"] * W * 2 + Pn * (W * 2 + 2 * m["ff"] * 2 + W * 4)), flops=layers * Pn * 3 * 2 * m["ff"] * W)
+        add(("moe_route", "moe_align", "moe_combine", "glu_clamped"), "election, order, sum, shared gate", phase, totals,
+            nbytes=layers * (rows * W * 2 + m["experts"] * W * 4 + Pn * W * 4 + 2 * rows * W * 2 + rows * 3 * m["shared_ff"] * 2))
+    return out
+
+
+def pironex_compare(a):
+    """Prefill and decode of the Pironex design beside Bufulorn of the same width, attention heads and recurrent sizes; one
+    JSON line. Device-timed like the benchmark's own points: one step of 2,048 prompt tokens (median of 5 after 3), decode
+    steps replayed from CUDA graphs (`--steps` steps a region, median region)."""
+    import torch
+    peaks = load_peaks()
+    n, B, blocks = 2048, a.batch, 2
+    gen = a.warmup + max(a.steps, MAX_TIMED_STEPS) + 64
+    sampler = ClockSampler()
+    sampler.start()
+    points = []
+    for key in a.pironex.split(","):
+        ps = PIRONEX_SIZES[key]
+        bs = BUFULORN_SIZES[ps["bufulorn"]]
+        point = {"sizes": key, "layers": 4 * blocks, "prompt_len": n, "batch": B}
+        for arch in ("pironex", "bufulorn"):
+            if arch == "pironex":
+                cfg, llm = make_pironex_engine(ps, blocks, B, n + gen, 8192)
+            else:
+                cfg, llm = make_bufulorn_engine(bs, blocks, B, n + gen, 8192)
+            g = torch.Generator().manual_seed(1)
+            prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for _ in range(B)]
+            ms_prefill = timed_prefill(llm, prompts[0], n)
+            ms_step, ctx_tokens, launches, regions = decode_device(llm, prompts, B, a.steps, a.warmup, n, gen)
+            prefill, decode = op_profile(llm, prompts, n, B)
+            e = {"prefill_tok_s": round(n / ms_prefill * 1e3, 1), "prefill_ms": round(ms_prefill, 3),
+                 "decode_tok_s": round(B / ms_step * 1e3, 1), "decode_ms_per_step": round(ms_step, 4),
+                 "decode_hbm_frac_of_measured": round(llm.runner.step_read_bytes(int(ctx_tokens)) / ms_step / 1e6 / peaks["hbm_gbs"], 3),
+                 "launches_per_decode_step": launches // a.steps,
+                 "ops_prefill_ms": {op: round(t, 4) for op, _, t in prefill}, "ops_decode_ms": {op: round(t, 4) for op, _, t in decode}}
+            e["kernels"] = pironex_roofline(ps, blocks, n, B, peaks, prefill, decode) if arch == "pironex" else \
+                bufulorn_roofline(bs, blocks, n, B, peaks, prefill, decode)
+            point[arch] = e
+            free_engine(llm)
+            del llm
+        points.append(point)
+    clocks = sampler.stop()
+    print(json.dumps({"metric": "Pironex beside Bufulorn at equal width, layer count, attention heads and recurrent sizes: "
+                                "prefill and decode tok/s",
+                      "dtype": "bf16", "data": "synthetic", "peaks": peaks, "points": points, "clocks": clocks, "run": run_record()}))
+    return 0
+
+
 def main():
     if "--kernel" in sys.argv[1:]:
         return kernel_case(sys.argv[1:])
@@ -1097,6 +1245,9 @@ def main():
     ap.add_argument("--bufulorn", default=None, metavar="SIZES", const="1b,3b", nargs="?",
                     help="instead of the benchmark's line: the Bufulorn design beside Lomopel at equal sizes (1b, 3b or both), "
                          "prefill and decode, with the time and roofline fraction of every kernel")
+    ap.add_argument("--pironex", default=None, metavar="SIZES", const="1b,3b", nargs="?",
+                    help="instead of the benchmark's line: the Pironex design beside Bufulorn at equal sizes (1b, 3b or both), "
+                         "prefill and decode, with the time and roofline fraction of every kernel")
     ap.add_argument("--tuning", action="append", default=[], metavar="FIELD=VALUE",
                     help="set a field of vllm_oxide_b200.tuning.TUNING (experiments)")
     ap.add_argument("--fold-rows", type=int, default=None, metavar="R",
@@ -1121,6 +1272,8 @@ def main():
         return lomopel_compare(a)
     if a.bufulorn:
         return bufulorn_compare(a)
+    if a.pironex:
+        return pironex_compare(a)
     prompt_len, gen_len = a.prompt_len, a.gen_len
     max_b = max(a.batch, 1 if (a.no_points or a.serve or a.timeline) else 64)
     if a.serve:

@@ -749,10 +749,13 @@ layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const 
     if (BY4) {
         for (int i = threadIdx.x * 4; i < h; i += 1024) {
             const float4 w4 = *reinterpret_cast<const float4*>(weight + i);
-            const float4 b4 = bias ? *reinterpret_cast<const float4*>(bias + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             const float4 r4 = *reinterpret_cast<const float4*>(row + i);
-            float4 y = make_float4((r4.x - mean) * inv * w4.x + b4.x, (r4.y - mean) * inv * w4.y + b4.y,
-                                   (r4.z - mean) * inv * w4.z + b4.z, (r4.w - mean) * inv * w4.w + b4.w);
+            float4 y = make_float4((r4.x - mean) * inv * w4.x, (r4.y - mean) * inv * w4.y, (r4.z - mean) * inv * w4.z,
+                                   (r4.w - mean) * inv * w4.w);
+            if (bias) {
+                const float4 b4 = *reinterpret_cast<const float4*>(bias + i);
+                y.x += b4.x; y.y += b4.y; y.z += b4.z; y.w += b4.w;
+            }
             if (d) {
                 const float4 x4 = *reinterpret_cast<const float4*>(x + i);
                 y.x += x4.x; y.y += x4.y; y.z += x4.z; y.w += x4.w;
