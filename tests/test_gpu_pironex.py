@@ -309,6 +309,32 @@ def test_pooled_window_attention_with_one_key_that_stands_out(dtype, H, G, D, DV
             want = plain.pooled_window_attention(torch.cat([torch.zeros(i, H, D, dtype=torch.float64), q.double()]), k.double()[:i + 1],
                                                  vv.double()[:i + 1], scale, cap, window, pool, rows=[i])[i].reshape(1, -1)
             assert _diff(out, want) < (3e-6 if dtype == torch.float32 else 2e-2), (i, mark)
+            if dtype == torch.bfloat16 and pool and D % 8 == 0 and DV % 8 == 0:
+                # the same row on the tensor cores, over pooled entries that `pool_blocks` leaves beside the caches
+                kp, vp = torch.full_like(kc, float("nan")), torch.full_like(vc, float("nan"))
+                kernels.pool_blocks(kc, vc, kp, vp, tables.to(DEV), _ints([0] * (i + 1)), _ints(list(range(i + 1))), pool)
+                out2 = torch.empty(1, H * DV, dtype=dtype, device=DEV)
+                kernels.attn_prefill_mma_any(q.reshape(1, -1).to(DEV), out2, kc, vc, tables.to(DEV), _ints([0, 1]), _ints([i]), 1, 1, H, G, D, DV,
+                                             scale, window, None, None, 1.0, softcap=cap, pooled=(kp, vp, pool))
+                assert _diff(out2, want) < 3e-2, (i, mark, "tensor cores")
+    if dtype == torch.bfloat16 and pool and D % 8 == 0 and DV % 8 == 0:
+        # a portion of 70 rows behind 80 cached tokens, and the same rows one by one: every row against the plain function
+        k, vv = k0.to(dtype), v.to(dtype)
+        q = (torch.randn(total, H, D) * 2).to(dtype)
+        _fill(kc, tables, 0, k, page)
+        _fill(vc, tables, 0, vv, page)
+        kp, vp = torch.full_like(kc, float("nan")), torch.full_like(vc, float("nan"))
+        kernels.pool_blocks(kc, vc, kp, vp, tables.to(DEV), _ints([0] * total), _ints(list(range(total))), pool)
+        want = plain.pooled_window_attention(q.double(), k.double(), vv.double(), scale, cap, window, pool, rows=range(80, total))[80:].reshape(70, -1)
+        out = torch.empty(70, H * DV, dtype=dtype, device=DEV)
+        kernels.attn_prefill_mma_any(q[80:].reshape(70, -1).to(DEV), out, kc, vc, tables.to(DEV), _ints([0, 70]), _ints([80]), 1, 70, H, G, D, DV,
+                                     scale, window, None, None, 1.0, softcap=cap, pooled=(kp, vp, pool))
+        assert _diff(out, want) < 3e-2
+        for i in (80, 95, 96, 149):
+            one = torch.empty(1, H * DV, dtype=dtype, device=DEV)
+            kernels.attn_prefill_mma_any(q[i].reshape(1, -1).to(DEV), one, kc, vc, tables.to(DEV), _ints([0, 1]), _ints([i]), 1, 1, H, G, D, DV,
+                                         scale, window, None, None, 1.0, softcap=cap, pooled=(kp, vp, pool))
+            assert _diff(one, want[i - 80:i - 79]) < 3e-2, i
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

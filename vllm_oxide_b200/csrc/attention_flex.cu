@@ -160,6 +160,49 @@ VOB_EXPORT int vob_flex_prep(const void* proj, int code, long ld, int q_off, int
 }
 
 // ---------------------------------------------------------------------------------------------
+// Pooled entries. A row at position p with (p + 1) % pool == 0 ends the block b = p / pool of `pool` tokens: the mean of
+// the block's cached keys and the mean of its cached values (float32 sums in token order, one division) are written to
+// kpool / vpool, which are laid out like the caches, at the place a token at position b would have (a request that holds
+// pages for its tokens holds that place too). Runs behind the kernel that wrote the step's keys and values; other rows
+// leave at once. Launch: grid (rows, kv heads), 128 threads.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+pool_blocks_kernel(const T* __restrict__ kcache, const T* __restrict__ vcache, T* __restrict__ kpool, T* __restrict__ vpool,
+                   const int* __restrict__ block_tables, int max_pages, const int* __restrict__ row_seq,
+                   const int* __restrict__ positions, int G, int D, int DV, int page_size, int pool) {
+    pdl_launch_dependents();
+    pdl_wait(63);
+    const int t = blockIdx.x, g = blockIdx.y;
+    const int pos = positions[t];
+    if (pos < 0 || (pos + 1) % pool != 0) return;
+    const int* bt = block_tables + (size_t)row_seq[t] * max_pages;
+    const int b = pos / pool, first = b * pool;
+    const size_t dst = (size_t)(bt[b / page_size] * G + g) * page_size + b % page_size;
+    const float inv = 1.0f / (float)pool;
+    for (int d = threadIdx.x; d < D + DV; d += 128) {
+        const bool key = d < D;
+        const T* src = key ? kcache : vcache;
+        const int w = key ? D : DV, c = key ? d : d - D;
+        float acc = 0.f;
+        for (int j = first; j <= pos; ++j)
+            acc += ld_f(src + ((size_t)(bt[j / page_size] * G + g) * page_size + j % page_size) * w + c);
+        st_f((key ? kpool : vpool) + dst * w + c, acc * inv);
+    }
+}
+
+VOB_EXPORT int vob_pool_blocks(const void* kcache, const void* vcache, void* kpool, void* vpool, int code, const int* block_tables,
+                               int max_pages, const int* row_seq, const int* positions, int T_rows, int G, int D, int DV, int page_size,
+                               int pool, cudaStream_t stream) {
+    if (T_rows <= 0) return 0;
+    if (G <= 0 || G > 65535 || D <= 0 || DV <= 0 || page_size <= 0 || max_pages <= 0 || pool <= 0) return VOB_ERR_BAD_ARG;
+    VOB_DISPATCH_ELEM(code, return vob_launch(pool_blocks_kernel<ElemT>, dim3(T_rows, G), dim3(128), 0, stream, (const ElemT*)kcache,
+                                              (const ElemT*)vcache, (ElemT*)kpool, (ElemT*)vpool, block_tables, max_pages, row_seq, positions,
+                                              G, D, DV, page_size, pool));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
 // General kernel: one warp per (row, head). Keys are visited in chunks of 32: each lane scores one
 // key against q held in shared memory, the warp agrees on the running maximum, then the 32 weighted
 // value rows are summed with lane l holding value features l, l + 32, ... Any D, DV up to 256, any

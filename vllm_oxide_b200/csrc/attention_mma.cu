@@ -80,16 +80,24 @@ __device__ __forceinline__ float tail_val(const AttnTail& t, long long row, int 
 //   r1, r2       [H] each: r1 * ln(1 + r2 * (i - j)) is taken off the score of key j for the query at i.
 // Scores leave in base-2 units (times log2 e), and the launchers' scale_log2 is not used by a shaped kernel. The struct
 // is a kernel parameter: what the inner loop reads of it comes from the constant bank and holds no register.
+//   pooled keys  (with a window, portion kernel only) beside the window's tokens a query at position p sees the first
+//                floor((p + 1 - window) / pool) entries of a second pair of caches, `kp` and `vp`: entry b, stored where a
+//                token at position b would be, is the mean key and the mean value of the tokens b * pool .. b * pool + pool - 1.
 struct ScoreShape {
     int chunk;
     float pre;            // q . k times this is tanh's argument (scale / softcap); without a cap, the score in base-2 units
     float cap_log2;       // softcap * log2 e, 0: no cap
     const float* r1;
     const float* r2;
+    const __nv_bfloat16* kp;      // pooled keys and values (null: none), laid out like the caches
+    const __nv_bfloat16* vp;
+    int pool;
 };
-inline ScoreShape make_shape(int chunk, float softcap, const float* r1, const float* r2, float scale) {
+inline ScoreShape make_shape(int chunk, float softcap, const float* r1, const float* r2, float scale, const void* kp = nullptr,
+                             const void* vp = nullptr, int pool = 0) {
     const float log2e = 1.4426950408889634f;
-    return ScoreShape{chunk, softcap > 0.f ? scale / softcap : scale * log2e, softcap > 0.f ? softcap * log2e : 0.f, r1, r2};
+    return ScoreShape{chunk, softcap > 0.f ? scale / softcap : scale * log2e, softcap > 0.f ? softcap * log2e : 0.f, r1, r2,
+                      (const __nv_bfloat16*)kp, (const __nv_bfloat16*)vp, pool};
 }
 // The distance bias of a thread's two rows: r1 and r2 of their heads (zero for a row that is no row of the request).
 struct RowShape {
@@ -431,7 +439,7 @@ attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     __nv_bfloat16* sK0 = sQ + BM * LD;
     __nv_bfloat16* sV0 = sK0 + 2 * BN * LD;
-    int* s_pages = reinterpret_cast<int*>(sV0 + 2 * BN * LDV);            // [max_pages]
+    int* s_pages = reinterpret_cast<int*>(sV0 + 2 * BN * LDV);            // [2 * max_pages]: the tokens' pages, then the pooled entries'
 
     const int G = H / KV;
     const int kvh = blockIdx.x, seq = blockIdx.y;
@@ -460,34 +468,34 @@ attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
     const int first_tok_pos = ctx + tile_row0 / G;
     const int chunk = SHAPED ? shape.chunk : 0;
     const int lo_blk = first_key(first_tok_pos, window, chunk);      // the block's first row reads furthest back
-    const int t_begin = lo_blk / BN, t_end = (hi + BN - 1) / BN;
-    const int page0 = lo_blk >> page_shift, page_end = ((hi - 1) >> page_shift) + 1;
-    for (int i = threadIdx.x; i < page_end - page0; i += NTHREADS) s_pages[i] = bt[page0 + i];
-    __syncthreads();
+    const int pool = SHAPED && shape.kp ? shape.pool : 0;
+    // pooled entries the block's last row sees (the most of all its rows)
+    const int hi_pool = pool > 0 && window > 0 && hi - window >= pool ? (hi - window) / pool : 0;
 
-    load_rows_padded<HD>(sK0, kc, D, s_pages, page0, kvh, KV, page_shift, t_begin * BN, lo_blk, hi);
-    load_rows_padded<HDV>(sV0, vc, DV, s_pages, page0, kvh, KV, page_shift, t_begin * BN, lo_blk, hi);
-    cp_async_commit();
-
-    int pos[2], lo[2], hd[2];
+    int pos[2], lo[2], hd[2], pos_p[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         int rr = tile_row0 + warp * 16 + (lane >> 2) + h * 8;
         pos[h] = rr < total_rows ? ctx + rr / G : -1;
         hd[h] = rr < total_rows ? kvh * G + rr % G : -1;
         lo[h] = first_key(pos[h], window, chunk);
+        // the last pooled entry this row sees (-1: none)
+        pos_p[h] = pool > 0 && pos[h] >= 0 && pos[h] + 1 - window >= pool ? (pos[h] + 1 - window) / pool - 1 : -1;
     }
     RowShape rs;
     if (SHAPED) rs = row_shape(shape, hd[0], hd[1]);
     int warp_last_pos = max(pos[0], pos[1]), warp_first_pos = min(pos[0], pos[1]), warp_max_lo = max(lo[0], lo[1]);
     int warp_min_lo = 0;                             // blocks of positions: the first key any row of the warp reads
     if (SHAPED) warp_min_lo = min(pos[0] < 0 ? 0x7fffffff : lo[0], pos[1] < 0 ? 0x7fffffff : lo[1]);
+    int warp_last_p = max(pos_p[0], pos_p[1]), warp_first_p = min(pos_p[0], pos_p[1]);
 #pragma unroll
     for (int x = 4; x < 32; x <<= 1) {
         warp_last_pos = max(warp_last_pos, __shfl_xor_sync(0xffffffffu, warp_last_pos, x));
         warp_first_pos = min(warp_first_pos, __shfl_xor_sync(0xffffffffu, warp_first_pos, x));
         warp_max_lo = max(warp_max_lo, __shfl_xor_sync(0xffffffffu, warp_max_lo, x));
         if (SHAPED) warp_min_lo = min(warp_min_lo, __shfl_xor_sync(0xffffffffu, warp_min_lo, x));
+        if (SHAPED) warp_last_p = max(warp_last_p, __shfl_xor_sync(0xffffffffu, warp_last_p, x));
+        if (SHAPED) warp_first_p = min(warp_first_p, __shfl_xor_sync(0xffffffffu, warp_first_p, x));
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[HDV / 8][4];
@@ -496,32 +504,54 @@ attn_prefill_mma_any_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
     uint32_t qf[HD / 16][4];
-
-    for (int t = t_begin; t < t_end; ++t) {
-        int buf = (t - t_begin) & 1;
+    // One walk over key tiles with one running softmax: first the tiles of pooled entries (where there are any), then the
+    // tiles of tokens. Both page lists sit in shared memory, the tokens' first.
+    const int tp_end = (hi_pool + BN - 1) / BN;
+    const int t_begin = lo_blk / BN, t_end = (hi + BN - 1) / BN;
+    const int page0 = lo_blk >> page_shift, page_end = ((hi - 1) >> page_shift) + 1;
+    int* s_pages_p = s_pages + (page_end - page0);
+    const int pages_p = hi_pool > 0 ? ((hi_pool - 1) >> page_shift) + 1 : 0;
+    for (int i = threadIdx.x; i < page_end - page0 + pages_p; i += NTHREADS) s_pages[i] = i < page_end - page0 ? bt[page0 + i] : bt[i - (page_end - page0)];
+    __syncthreads();
+    const int n_it = tp_end + (t_end - t_begin);
+    auto load_tile = [&](int it, int buf) {
+        if (SHAPED && it < tp_end) {
+            load_rows_padded<HD>(sK0 + buf * BN * LD, shape.kp, D, s_pages_p, 0, kvh, KV, page_shift, it * BN, 0, hi_pool);
+            load_rows_padded<HDV>(sV0 + buf * BN * LDV, shape.vp, DV, s_pages_p, 0, kvh, KV, page_shift, it * BN, 0, hi_pool);
+        } else {
+            const int t = t_begin + it - tp_end;
+            load_rows_padded<HD>(sK0 + buf * BN * LD, kc, D, s_pages, page0, kvh, KV, page_shift, t * BN, lo_blk, hi);
+            load_rows_padded<HDV>(sV0 + buf * BN * LDV, vc, DV, s_pages, page0, kvh, KV, page_shift, t * BN, lo_blk, hi);
+        }
+        cp_async_commit();
+    };
+    load_tile(0, 0);
+    for (int it = 0; it < n_it; ++it) {
+        const int buf = it & 1;
         __nv_bfloat16* sK = sK0 + buf * BN * LD;
         __nv_bfloat16* sV = sV0 + buf * BN * LDV;
         cp_async_wait<0>();
-        __syncthreads();                       // tile t (and Q) visible; everyone is done with tile t-1
-        if (t + 1 < t_end) {
-            load_rows_padded<HD>(sK0 + (buf ^ 1) * BN * LD, kc, D, s_pages, page0, kvh, KV, page_shift, (t + 1) * BN, lo_blk, hi);
-            load_rows_padded<HDV>(sV0 + (buf ^ 1) * BN * LDV, vc, DV, s_pages, page0, kvh, KV, page_shift, (t + 1) * BN, lo_blk, hi);
-            cp_async_commit();
-        }
-        if (t == t_begin) {
+        __syncthreads();                       // this tile (and Q) visible; everyone is done with the tile before
+        if (it + 1 < n_it) load_tile(it + 1, buf ^ 1);
+        if (it == 0) {
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk)
                 ldmatrix_x4(qf[kk], sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8);
         }
-        // nor has one whose rows all begin to read behind this tile's last key
-        if (t * BN <= warp_last_pos && (!SHAPED || (t + 1) * BN > warp_min_lo)) {
+        const bool pooled = SHAPED && it < tp_end;
+        const int t = pooled ? it : t_begin + it - tp_end;
+        const int w_last = pooled ? warp_last_p : warp_last_pos, w_first = pooled ? warp_first_p : warp_first_pos;
+        const int w_max_lo = pooled ? 0 : warp_max_lo, w_min_lo = pooled ? 0 : warp_min_lo;
+        const int lo_r[2] = {pooled ? 0 : lo[0], pooled ? 0 : lo[1]}, pos_r[2] = {pooled ? pos_p[0] : pos[0], pooled ? pos_p[1] : pos[1]};
+        // a tile behind the warp's last key needs no work, nor has one whose rows all begin to read behind this tile's last key
+        if (t * BN <= w_last && (!SHAPED || (t + 1) * BN > w_min_lo)) {
             float s[8][4];
             qk_tile<HD, 8>(s, qf, sK, 0);
             uint32_t pa[4][4];
-            if ((t + 1) * BN - 1 <= warp_first_pos && t * BN >= warp_max_lo)
-                softmax_step<8, HDV / 8, false, SHAPED>(s, pa, o, m, l, t * BN, lo, pos, scale_log2, &shape, &rs);
+            if ((t + 1) * BN - 1 <= w_first && t * BN >= w_max_lo)
+                softmax_step<8, HDV / 8, false, SHAPED>(s, pa, o, m, l, t * BN, lo_r, pos_r, scale_log2, &shape, &rs);
             else
-                softmax_step<8, HDV / 8, true, SHAPED>(s, pa, o, m, l, t * BN, lo, pos, scale_log2, &shape, &rs);
+                softmax_step<8, HDV / 8, true, SHAPED>(s, pa, o, m, l, t * BN, lo_r, pos_r, scale_log2, &shape, &rs);
             pv_tile<HDV, 4>(o, pa, sV, 0);
         }
     }
@@ -965,7 +995,7 @@ int launch_prefill_any(const void* q, long long q_stride, void* out, long long o
                        int H, int KV, int D, int DV, int page_size, int window, float scale, AttnTail tail, ScoreShape shape,
                        cudaStream_t stream) {
     static size_t configured = 0;
-    size_t smem = ((size_t)(64 + 2 * BN) * (HD + 8) + (size_t)2 * BN * (HDV + 8)) * sizeof(__nv_bfloat16) + (size_t)max_pages * sizeof(int);
+    size_t smem = ((size_t)(64 + 2 * BN) * (HD + 8) + (size_t)2 * BN * (HDV + 8)) * sizeof(__nv_bfloat16) + (size_t)2 * max_pages * sizeof(int);
     int e = ensure_smem(attn_prefill_mma_any_kernel<HD, HDV, SHAPED>, smem, &configured);
     if (e) return e;
     const long long row_tiles = ((long long)max_new * (H / KV) + 63) / 64;
@@ -1051,10 +1081,14 @@ VOB_EXPORT int vob_attn_prefill_shaped(const void* q, long long q_stride, void* 
                                        const int* context_lens, int S, int max_new, int H, int KV, int D, int DV, int page_size,
                                        int window, float scale, const float* sink, const void* gate, long long gate_stride,
                                        float out_scale, int chunk, float softcap, const float* r1, const float* r2,
-                                       cudaStream_t stream) {
+                                       const void* kpool, const void* vpool, int pool, cudaStream_t stream) {
     const AttnTail tail{sink, (const __nv_bfloat16*)gate, gate_stride, out_scale};
     if (chunk < 0 || softcap < 0.f || (r1 != nullptr) != (r2 != nullptr)) return VOB_ERR_BAD_ARG;
-    const ScoreShape shape = make_shape(chunk, softcap, r1, r2, scale);
+    // pooled entries (kpool, vpool laid out like the caches, `pool` tokens an entry) go with a window, without blocks of
+    // positions and without a distance bias
+    if (pool < 0 || (pool > 0) != (kpool != nullptr) || (kpool != nullptr) != (vpool != nullptr)) return VOB_ERR_BAD_ARG;
+    if (pool > 0 && (window <= 0 || chunk > 0 || r1)) return VOB_ERR_BAD_ARG;
+    const ScoreShape shape = make_shape(chunk, softcap, r1, r2, scale, kpool, vpool, pool);
     return prefill_any<true>(q, q_stride, out, out_stride, kcache, vcache, block_tables, max_pages, seq_starts, context_lens, S, max_new,
                              H, KV, D, DV, page_size, window, scale, tail, shape, stream);
 }

@@ -1518,6 +1518,32 @@ def flex_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, positions:
 
 
 @_timed
+def pool_blocks(kcache: torch.Tensor, vcache: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_tables: torch.Tensor,
+                row_seq: torch.Tensor, positions: torch.Tensor, pool: int) -> None:
+    """For every row whose position p ends a block of `pool` tokens ((p + 1) % pool == 0): the mean of the block's cached keys
+    and the mean of its cached values (float32 sums in token order) go to kpool and vpool, laid out like the caches, at the
+    place a token at position p // pool would have. Runs behind the kernel that wrote the step's keys and values."""
+    op = "pool_blocks"
+    _cuda(op, kcache, vcache, kpool, vpool, block_tables, row_seq, positions)
+    if kcache.dim() != 4 or vcache.dim() != 4 or kpool.shape != kcache.shape or vpool.shape != vcache.shape or kpool.dtype != kcache.dtype \
+            or vpool.dtype != kcache.dtype or vcache.dtype != kcache.dtype or kcache.shape[:3] != vcache.shape[:3]:
+        raise ShapeError(op, "caches [pages, heads, page, width] and pooled tensors of their shapes and type are needed")
+    for t in (kcache, vcache, kpool, vpool):
+        if not t.is_contiguous():
+            raise ShapeError(op, "caches and pooled tensors must be contiguous")
+    if pool <= 0:
+        raise ShapeError(op, f"a block of {pool} tokens")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or not block_tables.is_contiguous():
+        raise ShapeError(op, "block_tables must be contiguous int32 [requests, max_pages]")
+    T = positions.numel()
+    _int32_vec(positions, T, op, "positions")
+    _int32_vec(row_seq, T, op, "row_seq")
+    f = _fn("attention_flex", "vob_pool_blocks", [_P, _P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P])
+    _check(f(_ptr(kcache), _ptr(vcache), _ptr(kpool), _ptr(vpool), _code(kcache, op), _ptr(block_tables), block_tables.shape[1], _ptr(row_seq),
+             _ptr(positions), T, kcache.shape[1], kcache.shape[3], vcache.shape[3], kcache.shape[2], int(pool), _stream()), op)
+
+
+@_timed
 def flex_attention(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                    row_seq: torch.Tensor, positions: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
                    window: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
@@ -1696,13 +1722,28 @@ def attn_prefill_mma_any_supported(num_heads: int, num_kv_heads: int, dim: int, 
 @_timed
 def attn_prefill_mma_any(q, out, kcache, vcache, block_tables, seq_starts, context_lens, num_seqs: int, max_new: int,
                          num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0, sink=None, gate=None,
-                         out_scale: float = 1.0, chunk: int = 0, softcap: float = 0.0, dist_bias=None) -> None:
+                         out_scale: float = 1.0, chunk: int = 0, softcap: float = 0.0, dist_bias=None, pooled=None) -> None:
     """Tensor-core attention for portions of prompts and mixed batches (bfloat16) with keys of `dim` and values of `vdim`
     features: q [T, H * dim], out [T, H * vdim] (any row stride), kcache [pages, KV, page, dim], vcache [pages, KV, page, vdim].
     The tiles in shared memory are padded with zero columns to the sizes the kernel is built for. Everything else as
-    `attn_prefill_mma`. `chunk`, `softcap`, `dist_bias`: see `_score_shape` (the kernel built for shaped scores runs then)."""
+    `attn_prefill_mma`. `chunk`, `softcap`, `dist_bias`: see `_score_shape` (the kernel built for shaped scores runs then).
+    `pooled` = (kpool, vpool, pool), with a window: beside the window's tokens a query at position p sees the first
+    floor((p + 1 - window) / pool) entries of kpool and vpool (laid out like the caches, entry b where a token at position b
+    would be: the mean key and value of tokens b * pool .. b * pool + pool - 1, as `pool_blocks` leaves them)."""
     op = "attn_prefill_mma_any"
     shape = _score_shape(op, q, num_heads, chunk, softcap, dist_bias)
+    pool_args = (_P(0), _P(0), 0)
+    if pooled is not None:
+        kpool, vpool, pool = pooled
+        _cuda(op, q, kpool, vpool)
+        if kpool.shape != kcache.shape or vpool.shape != vcache.shape or kpool.dtype != kcache.dtype or vpool.dtype != vcache.dtype \
+                or not kpool.is_contiguous() or not vpool.is_contiguous():
+            raise ShapeError(op, "the pooled entries are laid out like the caches")
+        if pool <= 0 or window <= 0 or chunk or dist_bias is not None:
+            raise ShapeError(op, "pooled entries go with a window, without blocks of positions and without a distance bias")
+        pool_args = (_ptr(kpool), _ptr(vpool), int(pool))
+        if shape is None:
+            shape = (0, 0.0, _P(0), _P(0))
     if shape is None and not scale > 0:
         raise ShapeError(op, f"the score scale must be positive, got {scale}")
     _cuda(op, q, out, kcache, vcache, block_tables, seq_starts, context_lens)
@@ -1736,7 +1777,7 @@ def attn_prefill_mma_any(q, out, kcache, vcache, block_tables, seq_starts, conte
     if shape is None:
         _check(_fn("attention_mma", "vob_attn_prefill_mma_any", sig + [_P])(*args, _stream()), op)
     else:
-        _check(_fn("attention_mma", "vob_attn_prefill_shaped", sig + [_I, _F, _P, _P, _P])(*args, *shape, _stream()), op)
+        _check(_fn("attention_mma", "vob_attn_prefill_shaped", sig + [_I, _F, _P, _P, _P, _P, _I, _P])(*args, *shape, *pool_args, _stream()), op)
 
 
 def attn_prefill_sm100_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_pages: int) -> bool:

@@ -88,6 +88,11 @@ def _cache_keep(cfg: PironexConfig, j: int):
     return ("window", users[0].window)
 
 
+def _pooled_sizes(cfg: PironexConfig, j: int):
+    """The block sizes the cache that layer j writes must serve: those of all the layers that read it."""
+    return tuple(sorted({cfg.layers[i].attention.pool for i in cfg.cache_users(j)} - {0}))
+
+
 def build_pironex(cfg: PironexConfig, weights: WeightSet, ctx) -> ModelSpec:
     dt, dev = ctx.dtype, ctx.device
     eps, t = cfg.norm_eps, weights.take
@@ -105,7 +110,7 @@ def build_pironex(cfg: PironexConfig, weights: WeightSet, ctx) -> ModelSpec:
                                      a.kv_heads, a.dim, a.vdim, a.scale, window=a.window, rot_dims=a.rot_dims, rot_base=a.rot_base,
                                      softcap=a.softcap, shared_kv=not own, cache_keep=_cache_keep(cfg, owner), dtype=dt, device=dev,
                                      q_pre_norm=t(x + "q.norm"), k_pre_norm=t(x + "k.norm") if own else None, pre_norm_eps=eps,
-                                     pool=a.pool)
+                                     pool=a.pool, pooled_sizes=_pooled_sizes(cfg, owner))
             schedule.append(LayerCall(layer=i, cache=owner, write=own))
         elif layer.type == "mamba2":
             s = layer.ssm

@@ -16,7 +16,10 @@ as parameters:
                      projection, all heads at once, is divided by its root mean square and multiplied by that weight;
 * `pool`             (with `window`) beside the window's tokens a query sees one key and value for every block of `pool`
                      positions that lies wholly before the window: the means of the block's cached keys and values, in the
-                     same softmax (the cache then keeps every token);
+                     same softmax (the cache then keeps every token, and beside keys and values it holds, for every
+                     size in `pooled_sizes`, the pooled keys and values: entry b where token b's would be);
+* `pooled_sizes`     the block sizes the cache serves where several layers with blocks of different sizes read it
+                     (default: this layer's own `pool`); the layer that writes the cache pools for all of them;
 * `chunk`            a query sees only the keys of its own block of `chunk` positions, blocks counted from position 0
                      (pages of earlier blocks are given back);
 * `softcap`          score <- softcap * tanh(score / softcap);
@@ -58,7 +61,7 @@ class SoftmaxAttention(Mixer):
                  k_norm_weight: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0, dist_bias=None,
                  shared_kv: bool = False, cache_keep: Optional[Tuple[str, int]] = None, dtype=torch.bfloat16, device="cuda",
                  q_pre_norm: Optional[torch.Tensor] = None, k_pre_norm: Optional[torch.Tensor] = None,
-                 pre_norm_eps: Optional[float] = None, pool: int = 0):
+                 pre_norm_eps: Optional[float] = None, pool: int = 0, pooled_sizes: Optional[Tuple[int, ...]] = None):
         self.H, self.G, self.D, self.DV = int(heads), int(kv_heads), int(dim), int(vdim)
         self.shared_kv = bool(shared_kv)
         if self.shared_kv:
@@ -111,6 +114,10 @@ class SoftmaxAttention(Mixer):
         self.pool = int(pool) if pool else 0
         if self.pool < 0 or (self.pool and not self.window):
             raise ValueError(f"pooled blocks of {pool} go with a window")
+        self.pooled_sizes = tuple(int(x) for x in pooled_sizes) if pooled_sizes is not None else ((self.pool,) if self.pool else ())
+        if (self.pool and self.pool not in self.pooled_sizes) or any(x <= 0 for x in self.pooled_sizes) \
+                or len(set(self.pooled_sizes)) != len(self.pooled_sizes):
+            raise ValueError(f"the cache's block sizes {self.pooled_sizes} must be distinct, positive and hold this layer's {self.pool}")
         own = ("full", 0) if self.pool else ("window", self.window) if self.window else ("chunk", self.chunk) if self.chunk else ("full", 0)
         self.cache_keep = (str(cache_keep[0]), int(cache_keep[1])) if cache_keep is not None else own
         if self.cache_keep != own and self.cache_keep[0] != "full":
@@ -161,8 +168,8 @@ class SoftmaxAttention(Mixer):
 
     # ------------------------------------------------------------------ what the runtime asks
     def cache_spec(self) -> Optional[CacheSpec]:
-        return CacheSpec(kind=self.cache_keep[0], window=self.cache_keep[1],
-                         tensors=(PagedTensorSpec(self.G, self.D), PagedTensorSpec(self.G, self.DV)))
+        kv = (PagedTensorSpec(self.G, self.D), PagedTensorSpec(self.G, self.DV))
+        return CacheSpec(kind=self.cache_keep[0], window=self.cache_keep[1], tensors=kv * (1 + len(self.pooled_sizes)))
 
     def shared_buffer(self) -> Optional[Tuple[str, int]]:
         """(name, columns) of the step buffer this mixer writes or reads, or None."""
@@ -203,7 +210,9 @@ class SoftmaxAttention(Mixer):
         if dtype == torch.float32:
             return ("gemm_f32", "attention_flex")
         mods = ["gemm_sm100", "attention_flex"]
-        if self.tensor_core_sizes():
+        if self.pool and self.padded_tile_sizes():
+            mods += ["attention_mma"]
+        elif self.tensor_core_sizes():
             mods += ["attention_mma"] + ([] if self.window or self.gated else ["attention_sm100"])
         elif self.padded_tile_sizes():
             mods += ["attention_mma"]
@@ -227,6 +236,10 @@ class SoftmaxAttention(Mixer):
                           self.inv_freq, self.rot, self.unit_rms, self.eps, self.q_temp, self.mix_weight, v_first, self.v_mode, q,
                           None if self.shared_kv else kc, None if self.shared_kv else vc, self.H, self.G, self.D, self.DV,
                           self.q_norm_w, self.k_norm_w, self.q_pre_w, self.k_pre_w)
+        if cache.write:        # the blocks that this step's tokens complete, in every size the cache serves
+            for i, size in enumerate(self.pooled_sizes):
+                kernels.pool_blocks(kc, vc, cache.tensors[2 + 2 * i], cache.tensors[3 + 2 * i], ctx.block_tables[cache.group], ctx.row_seq,
+                                    ctx.positions, size)
         gate = proj[:, self.g_off:self.g_off + self.n_pre] if self.gated else None
         self.attend(q, pre_out, ctx, cache, gate, out_scale)
 
@@ -262,7 +275,16 @@ class SoftmaxAttention(Mixer):
                                              ctx.max_new, H, G, D, self.scale, self.window, self.sink, gate, out_scale)
                 return
         shaped = not self.plain_scores()
-        if self.pool:       # pooled blocks: the general kernel
+        if (self.pool and self.dtype == torch.bfloat16 and self.impl != "general" and self.dist_bias is None and ctx.max_new > 0
+                and kernels.attn_prefill_mma_any_supported(H, G, D, self.DV, page) and out.data_ptr() % 4 == 0 and out.stride(0) % 2 == 0):
+            # pooled blocks on the tensor cores: the padded portion kernel walks the pooled entries, then the window's tokens
+            # (steps of single tokens too: a tile then holds one token's heads)
+            i = self.pooled_sizes.index(self.pool)
+            kernels.attn_prefill_mma_any(q, out, kc, vc, bt, ctx.seq_starts, ctx.context_lens, ctx.seqs, ctx.max_new, H, G, D, self.DV,
+                                         self.scale, self.window, self.sink, gate, out_scale, softcap=self.softcap,
+                                         pooled=(cache.tensors[2 + 2 * i], cache.tensors[3 + 2 * i], self.pool))
+            return
+        if self.pool:       # pooled blocks, float32 or sizes the tensor cores do not take: the general kernel pools on its way
             kernels.flex_attention(q, out, kc, vc, bt, ctx.row_seq, ctx.positions, H, G, D, self.DV, self.scale, self.window, self.sink,
                                    gate, out_scale, self.chunk, self.softcap, self.dist_bias, self.pool)
             return
