@@ -1266,6 +1266,13 @@ def main():
         return 2
     a.warmup = max(a.warmup, 3)
     a.steps = max(a.steps, 1)
+    for kv in a.tuning:
+        from vllm_oxide_b200.tuning import TUNING
+        k, _, v = kv.partition("=")
+        if not hasattr(TUNING, k):
+            print(f"bench.py: TUNING has no field {k!r}")
+            return 2
+        setattr(TUNING, k, int(v))
     if a.rotepel:
         return rotepel_compare(a)
     if a.lomopel:
@@ -1287,13 +1294,6 @@ def main():
         return 2
 
     import torch
-    for kv in a.tuning:
-        from vllm_oxide_b200.tuning import TUNING
-        k, _, v = kv.partition("=")
-        if not hasattr(TUNING, k):
-            print(f"bench.py: TUNING has no field {k!r}")
-            return 2
-        setattr(TUNING, k, int(v))
     if a.fold_rows is not None:
         from vllm_oxide_b200.tuning import TUNING
         TUNING.few_rows = a.fold_rows

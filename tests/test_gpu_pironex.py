@@ -196,6 +196,24 @@ def test_layer_norm_without_bias_depth_average_and_clamped_gate():
         results.append(new.double())
         want = sum(w[j].double() * results[j] for j in range(n + 1))
         assert _diff(x, want) < 2e-6 and torch.equal(stack[:, n], new)
+    # the same sum, and a convolution's state moved on, done by the norm behind a sub-layer on its way
+    for dt in (torch.float32, torch.bfloat16):
+        for h in (42, 64):
+            T, slots, taps = 9, 3, 3
+            stack = torch.randn(T, slots, h, device=DEV)
+            stack2 = stack.clone()
+            resid, delta = torch.randn(T, h, device=DEV), torch.randn(T, h, device=DEV).to(dt)
+            resid2 = resid.clone()
+            w, dw = torch.randn(h, device=DEV), torch.randn(3, device=DEV)
+            cx = torch.randn(T, h, device=DEV).to(dt)
+            state = torch.randn(4, taps - 1, h, device=DEV)
+            state2 = state.clone()
+            pos, row_seq, starts, slots_ = _ints([5, 6, 7, 0, 3, 4, 5, 6, -1]), _ints([0, 0, 0, 1, 2, 2, 2, 2, 0]), _ints([0, 3, 4, 8]), _ints([2, 0, 3])
+            kernels.layernorm_add(resid, delta, w, None, 1e-5, depth=(stack, dw, 2), conv=(cx, state, row_seq, starts, slots_, pos))
+            kernels.layernorm_add(resid2, delta, w, None, 1e-5)
+            kernels.depth_average(stack2, resid2, dw, 2)
+            kernels.conv_state_update(cx, 0, state2, starts, slots_, 3)
+            assert torch.equal(resid, resid2) and torch.equal(stack, stack2) and torch.equal(state, state2)
     # the clamped gate: values beyond the limit on both sides of both halves
     for dt in (torch.float32, torch.bfloat16):
         gu = (torch.randn(6, 2 * 30 + 8, device=DEV) * 3).to(dt)
@@ -231,7 +249,7 @@ def test_causal_convolution_with_its_state_over_short_portions(dtype, taps, resi
         starts = _ints([0] + torch.tensor([n for _, n in step]).cumsum(0).tolist())
         ss = _ints([slots[r] for r, _ in step])
         out = torch.empty(rows.shape[0], C, dtype=torch.float32, device=DEV)
-        kernels.causal_conv(wide[:, :C], w, bias, state, pos, row_seq, starts, ss, len(step), out, residual=residual, act=act)
+        kernels.causal_conv(wide[:, :C], w.t().contiguous(), bias, state, pos, row_seq, starts, ss, len(step), out, residual=residual, act=act)
         if state is not None:
             kernels.conv_state_update(wide, 0, state, starts, ss, len(step))
         o = 0
@@ -249,7 +267,7 @@ def test_causal_convolution_with_its_state_over_short_portions(dtype, taps, resi
         state[0].zero_()
         x = torch.randn(2, C).to(dtype)
         out = torch.empty(2, C, dtype=torch.float32, device=DEV)
-        kernels.causal_conv(x.to(DEV), w, bias, state, _ints([0, 1]), _ints([0, 0]), _ints([0, 2]), _ints([0]), 1, out, residual=residual, act=act)
+        kernels.causal_conv(x.to(DEV), w.t().contiguous(), bias, state, _ints([0, 1]), _ints([0, 0]), _ints([0, 2]), _ints([0]), 1, out, residual=residual, act=act)
         want = plain.causal_conv(x.double(), w.double().cpu(), bias.double().cpu() if bias is not None else None) + (x.double() if residual else 0)
         assert _diff(out, plain.silu(want) if act == "silu" else want) < 3e-6
 
@@ -532,6 +550,28 @@ def test_portions_unequal_batches_and_reuse(tmp_path, name, dtype):
         else:
             err = _row_errors(got[k], alone)
             assert float(err.median()) < 1.5e-2 and float(err.quantile(0.9)) < 6e-2, (k, float(err.median()), float(err.quantile(0.9)))
+
+
+def test_the_norm_behind_a_sub_layer_doing_more_on_its_way_changes_nothing(tmp_path):
+    """`TUNING.norm_tail`: the convolutions' state and the sum over depth done by the norm kernel itself, bit for bit what
+    the separate kernels give, over portions, single tokens and a slot that is used again."""
+    from vllm_oxide_b200.replay.trace import TraceSession
+    from vllm_oxide_b200.tuning import TUNING
+    d = _model_dir(tmp_path, "A")
+    reqs = {"a": _tokens(40, 97, 1), "b": _tokens(9, 97, 2), "c": _tokens(17, 97, 3)}
+    schedule = [[("a", 2), ("b", 7)], [("a", 1), ("b", 2)], [("c", 3), ("a", 30)], [("a", 7), ("c", 14)]]
+    got = {}
+    before = TUNING.norm_tail
+    try:
+        for mode in (0, 1):
+            TUNING.norm_tail = mode
+            runner = _runner(d, "float32", page=8, pages=16, max_seqs=2)
+            got[mode] = _replay(TraceSession(runner), reqs, schedule)
+    finally:
+        TUNING.norm_tail = before
+    for k in reqs:
+        assert torch.equal(got[0][k], got[1][k]), k
+        assert _close(got[1][k], _plain_logits(d, reqs[k]), "float32"), k
 
 
 def test_the_stream_after_every_layer(tmp_path):

@@ -699,12 +699,32 @@ template <> __device__ __forceinline__ void st4_f<__nv_bfloat16>(__nv_bfloat16* 
     *reinterpret_cast<uint2*>(p) = a;
 }
 
+// What the kernel can do on its way behind resid[r] += LN(delta[r]) (a kernel parameter: what is not asked for costs nothing):
+//   * the stream as a weighted sum over depth (see depth_average_kernel, the same sums in the same order): the new row is
+//     filed as entry `depth_n` of `stack` [T, depth_slots, h] and replaced by sum_j depth_w[j] * entry j, j = 0 .. depth_n;
+//   * the last taps - 1 inputs of a short convolution that ran in front of the sub-layer (`conv_x` [T, h], what the
+//     convolution read, in delta's type): the block of a request's last row of the step leaves them in the request's state
+//     slot, new[m] = x_(n - (taps - 1) + m) if that row is of this step, else old[m + n] (m ascending, in place). Every
+//     kernel that read the old state has completed by now.
+struct NormTail {
+    float* stack;
+    const float* depth_w;
+    int depth_slots, depth_n;
+    const void* conv_x;
+    float* conv_state;
+    int taps;
+    const int* row_seq;
+    const int* seq_starts;
+    const int* state_slots;
+    const int* positions;
+};
+
 // BY4: the row's length is a multiple of 4 and every row starts where four features can be read at once; a thread
 // then takes four neighbouring features a turn (its partial sums run over them in order).
 template <typename TD, typename TO, bool BY4>
 __global__ void __launch_bounds__(256)
 layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ weight,
-                 const float* __restrict__ bias, const int* __restrict__ rows, TO* __restrict__ out, int h, float eps) {
+                 const float* __restrict__ bias, const int* __restrict__ rows, TO* __restrict__ out, int h, float eps, NormTail tail) {
     pdl_launch_dependents();
     pdl_wait(5);
     extern __shared__ __align__(16) float row[];
@@ -776,10 +796,69 @@ layernorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const 
             if (o) st_f(o + i, y);
         }
     }
+    if (tail.stack) {
+        __syncthreads();       // the row's new values, whoever wrote them
+        float* base = tail.stack + (size_t)r * tail.depth_slots * h;
+        const int dn = tail.depth_n;
+        if (BY4) {
+            for (int i = threadIdx.x * 4; i < h; i += 1024) {
+                const float4 cur = *reinterpret_cast<const float4*>(x + i);
+                *reinterpret_cast<float4*>(base + (size_t)dn * h + i) = cur;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                for (int j = 0; j < dn; ++j) {
+                    const float wj = tail.depth_w[j];
+                    const float4 e = *reinterpret_cast<const float4*>(base + (size_t)j * h + i);
+                    acc.x = fmaf(wj, e.x, acc.x); acc.y = fmaf(wj, e.y, acc.y); acc.z = fmaf(wj, e.z, acc.z); acc.w = fmaf(wj, e.w, acc.w);
+                }
+                const float wn = tail.depth_w[dn];
+                *reinterpret_cast<float4*>(x + i) = make_float4(fmaf(wn, cur.x, acc.x), fmaf(wn, cur.y, acc.y), fmaf(wn, cur.z, acc.z),
+                                                                fmaf(wn, cur.w, acc.w));
+            }
+        } else {
+            for (int i = threadIdx.x; i < h; i += blockDim.x) {
+                const float cur = x[i];
+                base[(size_t)dn * h + i] = cur;
+                float acc = 0.f;
+                for (int j = 0; j < dn; ++j) acc = fmaf(tail.depth_w[j], base[(size_t)j * h + i], acc);
+                x[i] = fmaf(tail.depth_w[dn], cur, acc);
+            }
+        }
+    }
+    if (tail.conv_state && tail.positions[r] >= 0) {
+        const int s = tail.row_seq[r];
+        const int r0 = tail.seq_starts[s], r1 = tail.seq_starts[s + 1];
+        if (r == r1 - 1) {
+            // a thread owns whole columns of the state: it reads a column's new entries (independent loads), then writes them
+            const int n = r1 - r0, keep = tail.taps - 1;
+            const TD* cx = reinterpret_cast<const TD*>(tail.conv_x);
+            float* st = tail.conv_state + (size_t)tail.state_slots[s] * keep * h;
+            if (keep <= 8) {
+#pragma unroll 2
+                for (int c = threadIdx.x; c < h; c += blockDim.x) {
+                    float v[8];
+#pragma unroll
+                    for (int m = 0; m < 8; ++m) {
+                        const int tau = n - keep + m;
+                        if (m < keep) v[m] = tau >= 0 ? ld_f(cx + (size_t)(r0 + tau) * h + c) : st[(size_t)(m + n) * h + c];
+                    }
+#pragma unroll
+                    for (int m = 0; m < 8; ++m)
+                        if (m < keep) st[(size_t)m * h + c] = v[m];
+                }
+            } else {
+                for (int c = threadIdx.x; c < h; c += blockDim.x)
+                    for (int m = 0; m < keep; ++m) {
+                        const int tau = n - keep + m;
+                        st[(size_t)m * h + c] = tau >= 0 ? ld_f(cx + (size_t)(r0 + tau) * h + c) : st[(size_t)(m + n) * h + c];
+                    }
+            }
+        }
+    }
 }
 
-VOB_EXPORT int vob_layernorm(float* resid, const void* delta, int delta_code, const float* weight, const float* bias,
-                             const int* rows, void* out, int out_code, int R, int h, float eps, cudaStream_t stream) {
+static int layernorm_launch(float* resid, const void* delta, int delta_code, const float* weight, const float* bias,
+                            const int* rows, void* out, int out_code, int R, int h, float eps, NormTail tail, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (h <= 0 || !weight || (delta && rows) || (!delta && !out)) return VOB_ERR_BAD_ARG;
     const size_t smem = (size_t)h * sizeof(float);
@@ -787,18 +866,37 @@ VOB_EXPORT int vob_layernorm(float* resid, const void* delta, int delta_code, co
     if (!delta) delta_code = VOB_F32;
     if (!out) out_code = VOB_F32;
     const bool by4 = h % 4 == 0 && ((((uintptr_t)resid) | ((uintptr_t)weight) | ((uintptr_t)bias)) & 15) == 0 && (((uintptr_t)delta) & 15) == 0 &&
-                     (((uintptr_t)out) & 15) == 0;
+                     (((uintptr_t)out) & 15) == 0 && (((uintptr_t)tail.stack) & 15) == 0;
 #define VOB_LN(TD_, TO_)                                                                                                             \
     return by4 ? vob_launch(layernorm_kernel<TD_, TO_, true>, dim3(R), dim3(256), smem, stream, resid, (const TD_*)delta, weight, bias, rows, \
-                            (TO_*)out, h, eps)                                                                                       \
+                            (TO_*)out, h, eps, tail)                                                                                 \
                : vob_launch(layernorm_kernel<TD_, TO_, false>, dim3(R), dim3(256), smem, stream, resid, (const TD_*)delta, weight, bias, rows, \
-                            (TO_*)out, h, eps)
+                            (TO_*)out, h, eps, tail)
     if (delta_code == VOB_F32 && out_code == VOB_F32) VOB_LN(float, float);
     if (delta_code == VOB_BF16 && out_code == VOB_BF16) VOB_LN(__nv_bfloat16, __nv_bfloat16);
     if (delta_code == VOB_F32 && out_code == VOB_BF16) VOB_LN(float, __nv_bfloat16);
     if (delta_code == VOB_BF16 && out_code == VOB_F32) VOB_LN(__nv_bfloat16, float);
 #undef VOB_LN
     return VOB_ERR_BAD_ARG;
+}
+
+VOB_EXPORT int vob_layernorm(float* resid, const void* delta, int delta_code, const float* weight, const float* bias,
+                             const int* rows, void* out, int out_code, int R, int h, float eps, cudaStream_t stream) {
+    return layernorm_launch(resid, delta, delta_code, weight, bias, rows, out, out_code, R, h, eps, NormTail{}, stream);
+}
+
+// resid[r] += LN(delta[r]) with what `NormTail` describes done on the way: the weighted sum over depth (stack non-null:
+// depth_w float32 [depth_n + 1], 0 < depth_n < depth_slots) and / or a convolution's state moved on (conv_state non-null:
+// float32 [slots, taps - 1, h]; conv_x [R, h] in delta's type; row_seq, positions int32 [R], seq_starts, state_slots per request).
+VOB_EXPORT int vob_layernorm_tail(float* resid, const void* delta, int delta_code, const float* weight, const float* bias, int R, int h,
+                                  float eps, float* stack, const float* depth_w, int depth_slots, int depth_n, const void* conv_x,
+                                  float* conv_state, int taps, const int* row_seq, const int* seq_starts, const int* state_slots,
+                                  const int* positions, cudaStream_t stream) {
+    if (!delta) return VOB_ERR_BAD_ARG;
+    if (stack && (!depth_w || depth_n <= 0 || depth_n >= depth_slots)) return VOB_ERR_BAD_ARG;
+    if (conv_state && (!conv_x || taps < 2 || !row_seq || !seq_starts || !state_slots || !positions)) return VOB_ERR_BAD_ARG;
+    const NormTail tail{stack, depth_w, depth_slots, depth_n, conv_x, conv_state, taps, row_seq, seq_starts, state_slots, positions};
+    return layernorm_launch(resid, delta, delta_code, weight, bias, nullptr, nullptr, 0, R, h, eps, tail, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -272,7 +272,7 @@ VOB_EXPORT int vob_conv_state_update(const void* proj, int code, long ld, int x_
 
 // ---------------------------------------------------------------------------------------------
 // A short causal convolution over time on each channel, with the last taps - 1 inputs of a request kept in its state slot:
-//   y[t, c] = (bias[c]) + sum_j w[c, j] * x[t - taps + 1 + j, c]      (x before this step's rows comes from the state,
+//   y[t, c] = (bias[c]) + sum_j w[j, c] * x[t - taps + 1 + j, c]      (w [taps, C]; x before this step's rows comes from the state,
 //                                                                     which is zero at a request's start)
 //   out[t, c] = act(y + (residual ? x[t, c] : 0)),   act: 0 none, 1 silu
 // x is a column range of a projection output [T, ld] in the activations' type; out [T, ld_out] of type TO. The state is
@@ -300,11 +300,74 @@ causal_conv_kernel(const T* __restrict__ x, long ld, int C, int taps, const floa
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;
         const float v = i - back >= 0 ? ld_f(x + (size_t)(t - back) * ld + c) : st[(size_t)(taps - 1 + i - back) * C + c];
-        acc = fmaf(w[(size_t)c * taps + j], v, acc);
+        acc = fmaf(w[(size_t)j * C + c], v, acc);
     }
     if (residual) acc += ld_f(x + (size_t)t * ld + c);
     if (act == 1) acc = acc / (1.0f + expf(-acc));
     st_f(out + (size_t)t * ld_out + c, acc);
+}
+
+// The same, VEC neighbouring channels a thread (16 bytes of x at a time): C, the row strides and the addresses allow it.
+template <typename T, typename TO, int VEC>
+__global__ void __launch_bounds__(128)
+causal_conv_vec_kernel(const T* __restrict__ x, long ld, int C, int taps, const float* __restrict__ w, const float* __restrict__ bias,
+                       const float* __restrict__ cstate, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                       const int* __restrict__ seq_starts, const int* __restrict__ state_slots, int residual, int act,
+                       TO* __restrict__ out, long ld_out) {
+    pdl_launch_dependents();
+    pdl_wait(49);
+    const int t = blockIdx.x, c = (blockIdx.y * 128 + threadIdx.x) * VEC;
+    if (c >= C) return;
+    float acc[VEC];
+    TO* o = out + (size_t)t * ld_out + c;
+    if (positions[t] < 0) {
+#pragma unroll
+        for (int k = 0; k < (int)(VEC * sizeof(TO) / 16); ++k) reinterpret_cast<uint4*>(o)[k] = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const int s = row_seq[t];
+    const int i = t - seq_starts[s];
+    const float* st = cstate ? cstate + (size_t)state_slots[s] * (taps - 1) * C : nullptr;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    float cur[VEC];
+    for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        float v[VEC];
+        if (i - back >= 0) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t - back) * ld + c);
+            const T* rv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = ld_f(rv + e);
+        } else {
+            const float* sp = st + (size_t)(taps - 1 + i - back) * C + c;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v[e] = sp[e];
+        }
+        const float4* wj = reinterpret_cast<const float4*>(w + (size_t)j * C + c);      // C and c are multiples of 4
+#pragma unroll
+        for (int e4 = 0; e4 < VEC / 4; ++e4) {
+            const float4 w4 = wj[e4];
+            acc[4 * e4] = fmaf(w4.x, v[4 * e4], acc[4 * e4]);
+            acc[4 * e4 + 1] = fmaf(w4.y, v[4 * e4 + 1], acc[4 * e4 + 1]);
+            acc[4 * e4 + 2] = fmaf(w4.z, v[4 * e4 + 2], acc[4 * e4 + 2]);
+            acc[4 * e4 + 3] = fmaf(w4.w, v[4 * e4 + 3], acc[4 * e4 + 3]);
+        }
+        if (back == 0) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) cur[e] = v[e];
+        }
+    }
+    __align__(16) TO ov[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+        float a = acc[e];
+        if (residual) a += cur[e];
+        if (act == 1) a = a / (1.0f + expf(-a));
+        st_f(ov + e, a);
+    }
+#pragma unroll
+    for (int k = 0; k < (int)(VEC * sizeof(TO) / 16); ++k) reinterpret_cast<uint4*>(o)[k] = reinterpret_cast<const uint4*>(ov)[k];
 }
 
 VOB_EXPORT int vob_causal_conv(const void* x, int code, long ld, int C, int taps, const float* w, const float* bias, const float* cstate,
@@ -313,12 +376,18 @@ VOB_EXPORT int vob_causal_conv(const void* x, int code, long ld, int C, int taps
     if (T <= 0) return 0;
     if (C <= 0 || taps < 1 || !w || (taps > 1 && !cstate) || (act != 0 && act != 1) || (C + 127) / 128 > 65535) return VOB_ERR_BAD_ARG;
     const dim3 grid(T, (C + 127) / 128);
-#define VOB_CONV(T_, TO_)                                                                                                     \
-    return vob_launch(causal_conv_kernel<T_, TO_>, grid, dim3(128), 0, stream, (const T_*)x, ld, C, taps, w, bias, cstate, positions, \
-                      row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out)
-    if (code == VOB_F32 && out_code == VOB_F32) VOB_CONV(float, float);
-    if (code == VOB_BF16 && out_code == VOB_BF16) VOB_CONV(__nv_bfloat16, __nv_bfloat16);
-    if (code == VOB_BF16 && out_code == VOB_F32) VOB_CONV(__nv_bfloat16, float);
+    const int vec = code == VOB_BF16 ? 8 : 4;
+    const int out_vec = out_code == VOB_BF16 ? 8 : 4;
+    const bool by16 = C % vec == 0 && ld % vec == 0 && (((uintptr_t)x) & 15) == 0 && ld_out % out_vec == 0 && (((uintptr_t)out) & 15) == 0 &&
+                      (((uintptr_t)w) & 15) == 0;
+#define VOB_CONV(T_, TO_, V_)                                                                                                 \
+    return by16 ? vob_launch(causal_conv_vec_kernel<T_, TO_, V_>, dim3(T, (C / V_ + 127) / 128), dim3(128), 0, stream, (const T_*)x, ld, C, \
+                             taps, w, bias, cstate, positions, row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out) \
+                : vob_launch(causal_conv_kernel<T_, TO_>, grid, dim3(128), 0, stream, (const T_*)x, ld, C, taps, w, bias, cstate,  \
+                             positions, row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out)
+    if (code == VOB_F32 && out_code == VOB_F32) VOB_CONV(float, float, 4);
+    if (code == VOB_BF16 && out_code == VOB_BF16) VOB_CONV(__nv_bfloat16, __nv_bfloat16, 8);
+    if (code == VOB_BF16 && out_code == VOB_F32) VOB_CONV(__nv_bfloat16, float, 8);
 #undef VOB_CONV
     return VOB_ERR_BAD_ARG;
 }

@@ -258,11 +258,48 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
 
 @_timed
 def layernorm_add(resid: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,
-                  copy: Optional[torch.Tensor] = None) -> None:
+                  copy: Optional[torch.Tensor] = None, depth=None, conv=None) -> None:
     """resid += LN(delta) with LN(z) = (z - mean) / sqrt(mean((z - mean)^2) + eps) * weight + bias; `copy` ([T, h] in the
-    activations' type), if given, receives the new residual."""
+    activations' type), if given, receives the new residual. On the way, where asked for (not together with `copy`):
+    `depth` = (stack float32 [T, slots, h], weights float32 [n + 1], n): what `depth_average` does with the new residual;
+    `conv` = (conv_x [T, h] of delta's type, conv_state float32 [slots, taps - 1, h], row_seq, seq_starts, state_slots,
+    positions): what `conv_state_update` does for a convolution that read conv_x in front of the sub-layer."""
     op = "layernorm_add"
     _cuda(op, resid, delta, weight, bias, copy)
+    if depth is not None or conv is not None:
+        if copy is not None:
+            raise ShapeError(op, "the residual's copy and the work on the way do not go together")
+        T, h = resid.shape
+        if resid.dtype != torch.float32 or resid.dim() != 2 or not resid.is_contiguous() or delta.shape != resid.shape or not delta.is_contiguous():
+            raise ShapeError(op, f"a contiguous float32 residual [T, h] and a contiguous delta of its shape are needed")
+        _f32_vec(weight, h, op, "weight")
+        _f32_vec(bias, h, op, "bias")
+        if h * 4 > 48 * 1024:
+            raise ShapeError(op, f"width {h} is beyond this kernel's limit of {48 * 1024 // 4}")
+        stack = dw = cx = cs = rs = ss = sl = ps = None
+        slots = n = taps = 0
+        if depth is not None:
+            stack, dw, n = depth
+            _cuda(op, resid, stack, dw)
+            if stack.dtype != torch.float32 or stack.dim() != 3 or stack.shape[0] != T or stack.shape[2] != h or not stack.is_contiguous() \
+                    or not 0 < n < stack.shape[1]:
+                raise ShapeError(op, f"stack must be contiguous float32 [{T}, > {n}, {h}], got {stack.dtype} {list(stack.shape)}")
+            _f32_vec(dw, n + 1, op, "depth weights")
+            slots = stack.shape[1]
+        if conv is not None:
+            cx, cs, rs, ss, sl, ps = conv
+            _cuda(op, resid, cx, cs, rs, ss, sl, ps)
+            if cx.shape != resid.shape or cx.dtype != delta.dtype or not cx.is_contiguous():
+                raise ShapeError(op, f"conv_x must be contiguous {delta.dtype} {list(resid.shape)}, got {cx.dtype} {list(cx.shape)}")
+            if cs.dtype != torch.float32 or cs.dim() != 3 or cs.shape[2] != h or cs.shape[1] < 1 or not cs.is_contiguous():
+                raise ShapeError(op, f"conv_state must be contiguous float32 [slots, taps - 1, {h}], got {cs.dtype} {list(cs.shape)}")
+            taps = cs.shape[1] + 1
+            _int32_vec(rs, T, op, "row_seq")
+            _int32_vec(ps, T, op, "positions")
+        f = _fn("elementwise", "vob_layernorm_tail", [_P, _P, _I, _P, _P, _I, _I, _F, _P, _P, _I, _I, _P, _P, _I, _P, _P, _P, _P, _P])
+        _check(f(_ptr(resid), _ptr(delta), _code(delta, op), _ptr(weight), _ptr(bias), T, h, float(eps), _ptr(stack), _ptr(dw), slots, int(n),
+                 _ptr(cx), _ptr(cs), taps, _ptr(rs), _ptr(ss), _ptr(sl), _ptr(ps), _stream()), op)
+        return
     if resid.dtype != torch.float32 or resid.dim() != 2 or not resid.is_contiguous():
         raise ShapeError(op, f"the residual must be contiguous float32 [T, h], got {resid.dtype} {list(resid.shape)}")
     T, h = resid.shape
@@ -1077,7 +1114,8 @@ def conv_state_update(proj: torch.Tensor, x_off: int, conv_state: torch.Tensor, 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], conv_state: Optional[torch.Tensor],
                 positions: torch.Tensor, row_seq: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
                 out: torch.Tensor, residual: bool = False, act: str = "none") -> None:
-    """A short causal convolution over time on each channel: y[t, c] = bias[c] + sum_j weight[c, j] * x[t - taps + 1 + j, c],
+    """A short causal convolution over time on each channel: y[t, c] = bias[c] + sum_j weight[j, c] * x[t - taps + 1 + j, c]
+    (weight float32 [taps, C]: tap by tap, the last row the current token's),
     inputs before the step's rows taken from `conv_state` (float32 [slots, taps - 1, C], the request's last inputs; zero at its
     start); out = act(y + x) with `residual`, act(y) without; act "none" or "silu". x [T, C] (a column range of a projection,
     any row stride), out [T, C] in x's type or float32. The state is only read: `conv_state_update` moves it on afterwards."""
@@ -1086,9 +1124,9 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     _rows_2d(x, op, "x")
     _rows_2d(out, op, "out")
     T, C = x.shape
-    if weight.dtype != torch.float32 or weight.dim() != 2 or weight.shape[0] != C or not weight.is_contiguous():
-        raise ShapeError(op, f"weight must be contiguous float32 [{C}, taps], got {weight.dtype} {list(weight.shape)}")
-    taps = weight.shape[1]
+    if weight.dtype != torch.float32 or weight.dim() != 2 or weight.shape[1] != C or not weight.is_contiguous():
+        raise ShapeError(op, f"weight must be contiguous float32 [taps, {C}], got {weight.dtype} {list(weight.shape)}")
+    taps = weight.shape[0]
     _f32_vec(bias, C, op, "bias")
     if taps > 1 and (conv_state is None or conv_state.dtype != torch.float32 or conv_state.dim() != 3 or not conv_state.is_contiguous()
                      or conv_state.shape[1:] != (taps - 1, C)):

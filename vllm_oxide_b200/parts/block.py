@@ -18,6 +18,7 @@ from typing import Optional
 
 import torch
 
+from ..tuning import TUNING
 from .base import FeedForward, FoldedState, LayerCache, Mixer, Norm, StateSpec, StepContext, aligned
 
 
@@ -220,11 +221,12 @@ class SandwichBlock:
         if canon2 is not None and feed_forward is None:
             raise ValueError("a convolution in front of a feed-forward that is not there")
         f32 = dict(device=device, dtype=torch.float32)
-        self.canon1 = canon1.to(**f32).contiguous() if canon1 is not None else None
-        self.canon2 = canon2.to(**f32).contiguous() if canon2 is not None else None
-        for c in (self.canon1, self.canon2):
+        for c in (canon1, canon2):
             if c is not None and (c.dim() != 2 or c.shape[1] < 1):
                 raise ValueError(f"a convolution's weights are [width, taps], got {list(c.shape)}")
+        # kept tap by tap ([taps, width]), as the kernel reads them
+        self.canon1 = canon1.to(**f32).t().contiguous() if canon1 is not None else None
+        self.canon2 = canon2.to(**f32).t().contiguous() if canon2 is not None else None
         self.depth_weights = depth_weights.to(**f32).contiguous() if depth_weights is not None else None
         self.depth_index, self.depth_slots, self.depth_name = int(depth_index), int(depth_slots), depth_name
         if self.depth_weights is not None and (self.depth_weights.shape != (self.depth_index + 2,) or self.depth_slots < self.depth_index + 2):
@@ -236,11 +238,11 @@ class SandwichBlock:
         return [p for p in (self.norm1, self.mixer, self.post1, self.norm2, self.feed_forward, self.post2) if p is not None]
 
     def _own_states(self):
-        return [c for c in (self.canon1, self.canon2) if c is not None and c.shape[1] > 1]
+        return [c for c in (self.canon1, self.canon2) if c is not None and c.shape[0] > 1]
 
     def state_spec(self):
         """The convolutions' last inputs (one tensor each, [taps - 1, width]), then the mixer's own state."""
-        own = [StateSpec((c.shape[1] - 1, c.shape[0]), torch.float32) for c in self._own_states()]
+        own = [StateSpec((c.shape[0] - 1, c.shape[1]), torch.float32) for c in self._own_states()]
         ms = self.mixer.state_spec()
         ms = [] if ms is None else list(ms) if isinstance(ms, (tuple, list)) else [ms]
         return tuple(own + ms) if own or ms else None
@@ -267,17 +269,21 @@ class SandwichBlock:
         return False
 
     def _read(self, norm: Norm, canon, conv_state, resid, ctx: StepContext):
-        """What a sub-layer reads: the normed residual, with its convolution added where there is one."""
+        """What a sub-layer reads: the normed residual, with its convolution added where there is one. Returns it and what the
+        norm behind the sub-layer is to do on its way: move the convolution's state on (every read of the old one is over then)."""
         from .. import kernels
         h = norm.forward(resid, None, ctx)
         if canon is None:
-            return h
+            return h, None
         hc = ctx.alloc(h.shape)
         kernels.causal_conv(h, canon, None, conv_state, ctx.positions, ctx.row_seq, ctx.seq_starts, ctx.state_slots, ctx.seqs, hc,
                             residual=True)
-        if conv_state is not None:
+        if conv_state is None:
+            return hc, None
+        if not TUNING.norm_tail:
             kernels.conv_state_update(h, 0, conv_state, ctx.seq_starts, ctx.state_slots, ctx.seqs)
-        return hc
+            return hc, None
+        return hc, (h, conv_state, ctx.row_seq, ctx.seq_starts, ctx.state_slots, ctx.positions)
 
     def forward(self, resid: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache: Optional[LayerCache], state, out: torch.Tensor, pending_scale: Optional[torch.Tensor] = None):
@@ -287,22 +293,26 @@ class SandwichBlock:
         ws = ctx.workspace
         states = list(state) if isinstance(state, (tuple, list)) else [] if state is None else [state]
         own = [states.pop(0) for _ in self._own_states()]
-        cs1 = own.pop(0) if self.canon1 is not None and self.canon1.shape[1] > 1 else None
-        cs2 = own.pop(0) if self.canon2 is not None and self.canon2.shape[1] > 1 else None
+        cs1 = own.pop(0) if self.canon1 is not None and self.canon1.shape[0] > 1 else None
+        cs2 = own.pop(0) if self.canon2 is not None and self.canon2.shape[0] > 1 else None
         ms = self.mixer.state_spec()
         mixer_state = None if ms is None else tuple(states) if isinstance(ms, (tuple, list)) else states[0]
-        stack = None
+        depth = None
         if self.depth_weights is not None:
             stack = ctx.shared[self.depth_name].view(resid.shape[0], self.depth_slots, resid.shape[1])
             if self.depth_index == 0:
                 kernels.depth_average(stack, resid, None, 0)
+            # the sum over depth rides on the block's last norm
+            depth = (stack, self.depth_weights, self.depth_index + 1) if TUNING.norm_tail else None
         with ws.scope():
-            m = self.mixer.forward(self._read(self.norm1, self.canon1, cs1, resid, ctx), ctx, cache, mixer_state)
-            self.post1.add_normed(resid, m, None)
+            x, conv = self._read(self.norm1, self.canon1, cs1, resid, ctx)
+            m = self.mixer.forward(x, ctx, cache, mixer_state)
+            self.post1.add_normed(resid, m, None, depth=depth if self.feed_forward is None else None, conv=conv)
         if self.feed_forward is not None:
             with ws.scope():
-                f = self.feed_forward.forward(self._read(self.norm2, self.canon2, cs2, resid, ctx), ctx)
-                self.post2.add_normed(resid, f, None)
-        if stack is not None:
+                x, conv = self._read(self.norm2, self.canon2, cs2, resid, ctx)
+                f = self.feed_forward.forward(x, ctx)
+                self.post2.add_normed(resid, f, None, depth=depth, conv=conv)
+        if self.depth_weights is not None and depth is None:
             kernels.depth_average(stack, resid, self.depth_weights, self.depth_index + 1)
         return None

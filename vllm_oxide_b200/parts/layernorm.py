@@ -46,6 +46,7 @@ class LayerNorm(Norm):
         kernels.layernorm_rows(resid, self.weight, self.bias, self.eps, out, rows[:n] if rows is not None else None)
         return out
 
-    def add_normed(self, resid: torch.Tensor, result: torch.Tensor, copy: Optional[torch.Tensor] = None) -> None:
-        """resid += LN(result); `copy`, if given, receives the new residual in its own type."""
-        kernels.layernorm_add(resid, result, self.weight, self.bias, self.eps, copy)
+    def add_normed(self, resid: torch.Tensor, result: torch.Tensor, copy: Optional[torch.Tensor] = None, depth=None, conv=None) -> None:
+        """resid += LN(result); `copy`, if given, receives the new residual in its own type. `depth`, `conv`: work the kernel
+        does on its way (see `kernels.layernorm_add`)."""
+        kernels.layernorm_add(resid, result, self.weight, self.bias, self.eps, copy, depth=depth, conv=conv)

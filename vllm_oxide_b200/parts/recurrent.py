@@ -301,7 +301,7 @@ class StateSpace(Mixer):
         self.w_in = to_compute(w_in, dtype, device)
         self.w_o = to_compute(wo, dtype, device)
         f32 = dict(device=device, dtype=torch.float32)
-        self.conv_w, self.conv_b = conv_w.to(**f32).contiguous(), conv_b.to(**f32).contiguous()
+        self.conv_w, self.conv_b = conv_w.to(**f32).t().contiguous(), conv_b.to(**f32).contiguous()     # tap by tap, as the kernel reads them
         self.dt_bias, self.a_log, self.d_skip = dt_bias.to(**f32).contiguous(), a_log.to(**f32).contiguous(), d_skip.to(**f32).contiguous()
         self.norm_weight = norm_weight.to(**f32).contiguous()
         self.eps, self.hidden, self.dtype = float(eps), hidden, dtype
