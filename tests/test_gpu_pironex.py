@@ -263,6 +263,20 @@ def test_causal_convolution_with_its_state_over_short_portions(dtype, taps, resi
         if act == "silu":
             want = plain.silu(want)
         assert _diff(torch.cat(got[r]), want) < 3e-6, r
+    if state is not None:
+        # a step in which every request brings one token: the kernel moves the state on itself, bit for bit as the two kernels do
+        for width in (C, 40):       # channels one by one, and 16 bytes a thread
+            st_a = torch.randn(3, taps - 1, width, device=DEV)
+            st_b = st_a.clone()
+            x = torch.randn(2, width).to(dtype).to(DEV)
+            wt = torch.randn(taps, width, device=DEV)
+            b2 = torch.randn(width, device=DEV) if bias is not None else None
+            args = (_ints([7, 3]), _ints([0, 1]), _ints([0, 1, 2]), _ints([2, 0]), 2)
+            out_a, out_b = (torch.empty(2, width, dtype=dtype, device=DEV) for _ in range(2))
+            kernels.causal_conv(x, wt, b2, st_a, *args, out_a, residual=residual, act=act)
+            kernels.conv_state_update(x, 0, st_a, args[2], args[3], 2)
+            kernels.causal_conv(x, wt, b2, st_b, *args, out_b, residual=residual, act=act, single=True)
+            assert torch.equal(out_a, out_b) and torch.equal(st_a, st_b)
     if state is not None:       # a new request in slot 0 starts from zeros
         state[0].zero_()
         x = torch.randn(2, C).to(dtype)

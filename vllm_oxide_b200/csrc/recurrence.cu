@@ -276,15 +276,16 @@ VOB_EXPORT int vob_conv_state_update(const void* proj, int code, long ld, int x_
 //                                                                     which is zero at a request's start)
 //   out[t, c] = act(y + (residual ? x[t, c] : 0)),   act: 0 none, 1 silu
 // x is a column range of a projection output [T, ld] in the activations' type; out [T, ld_out] of type TO. The state is
-// only read here: vob_conv_state_update moves it on behind this kernel. Rows with a negative position (padding) get zeros.
+// only read here (but see `single`): vob_conv_state_update moves it on behind this kernel. Rows with a negative position
+// (padding) get zeros.
 // Launch: grid (tokens, ceil(C / 128)), 128 threads, one channel each; the sum runs over the taps in order.
 // ---------------------------------------------------------------------------------------------
 template <typename T, typename TO>
 __global__ void __launch_bounds__(128)
 causal_conv_kernel(const T* __restrict__ x, long ld, int C, int taps, const float* __restrict__ w, const float* __restrict__ bias,
-                   const float* __restrict__ cstate, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                   float* cstate, const int* __restrict__ positions, const int* __restrict__ row_seq,
                    const int* __restrict__ seq_starts, const int* __restrict__ state_slots, int residual, int act,
-                   TO* __restrict__ out, long ld_out) {
+                   TO* __restrict__ out, long ld_out, int single) {
     pdl_launch_dependents();
     pdl_wait(49);
     const int t = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
@@ -295,12 +296,16 @@ causal_conv_kernel(const T* __restrict__ x, long ld, int C, int taps, const floa
     }
     const int s = row_seq[t];
     const int i = t - seq_starts[s];                 // this row's place among the request's rows of the step
-    const float* st = cstate ? cstate + (size_t)state_slots[s] * (taps - 1) * C : nullptr;
+    float* st = cstate ? cstate + (size_t)state_slots[s] * (taps - 1) * C : nullptr;
     float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;
         const float v = i - back >= 0 ? ld_f(x + (size_t)(t - back) * ld + c) : st[(size_t)(taps - 1 + i - back) * C + c];
         acc = fmaf(w[(size_t)j * C + c], v, acc);
+    }
+    if (single && st) {      // the request's only row: this thread alone touches its channel of the state, and moves it on
+        for (int m = 0; m + 2 < taps; ++m) st[(size_t)m * C + c] = st[(size_t)(m + 1) * C + c];
+        st[(size_t)(taps - 2) * C + c] = ld_f(x + (size_t)t * ld + c);
     }
     if (residual) acc += ld_f(x + (size_t)t * ld + c);
     if (act == 1) acc = acc / (1.0f + expf(-acc));
@@ -311,9 +316,9 @@ causal_conv_kernel(const T* __restrict__ x, long ld, int C, int taps, const floa
 template <typename T, typename TO, int VEC>
 __global__ void __launch_bounds__(128)
 causal_conv_vec_kernel(const T* __restrict__ x, long ld, int C, int taps, const float* __restrict__ w, const float* __restrict__ bias,
-                       const float* __restrict__ cstate, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                       float* cstate, const int* __restrict__ positions, const int* __restrict__ row_seq,
                        const int* __restrict__ seq_starts, const int* __restrict__ state_slots, int residual, int act,
-                       TO* __restrict__ out, long ld_out) {
+                       TO* __restrict__ out, long ld_out, int single) {
     pdl_launch_dependents();
     pdl_wait(49);
     const int t = blockIdx.x, c = (blockIdx.y * 128 + threadIdx.x) * VEC;
@@ -327,7 +332,7 @@ causal_conv_vec_kernel(const T* __restrict__ x, long ld, int C, int taps, const 
     }
     const int s = row_seq[t];
     const int i = t - seq_starts[s];
-    const float* st = cstate ? cstate + (size_t)state_slots[s] * (taps - 1) * C : nullptr;
+    float* st = cstate ? cstate + (size_t)state_slots[s] * (taps - 1) * C : nullptr;
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[e] = bias ? bias[c + e] : 0.f;
     float cur[VEC];
@@ -356,7 +361,20 @@ causal_conv_vec_kernel(const T* __restrict__ x, long ld, int C, int taps, const 
         if (back == 0) {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) cur[e] = v[e];
+        } else if (single && st) {
+            // the request's only row: every input before it came from the state, and this thread alone touches its channels
+            // of it; what it has just read moves one place down (the oldest leaves)
+            if (back < taps - 1) {
+                float* sp = st + (size_t)(taps - 2 - back) * C + c;
+#pragma unroll
+                for (int e4 = 0; e4 < VEC / 4; ++e4) reinterpret_cast<float4*>(sp)[e4] = make_float4(v[4 * e4], v[4 * e4 + 1], v[4 * e4 + 2], v[4 * e4 + 3]);
+            }
         }
+    }
+    if (single && st) {
+        float* sp = st + (size_t)(taps - 2) * C + c;
+#pragma unroll
+        for (int e4 = 0; e4 < VEC / 4; ++e4) reinterpret_cast<float4*>(sp)[e4] = make_float4(cur[4 * e4], cur[4 * e4 + 1], cur[4 * e4 + 2], cur[4 * e4 + 3]);
     }
     __align__(16) TO ov[VEC];
 #pragma unroll
@@ -370,21 +388,23 @@ causal_conv_vec_kernel(const T* __restrict__ x, long ld, int C, int taps, const 
     for (int k = 0; k < (int)(VEC * sizeof(TO) / 16); ++k) reinterpret_cast<uint4*>(o)[k] = reinterpret_cast<const uint4*>(ov)[k];
 }
 
-VOB_EXPORT int vob_causal_conv(const void* x, int code, long ld, int C, int taps, const float* w, const float* bias, const float* cstate,
+// `single`: the caller knows that every request brings exactly one row; the kernel then also moves the state on (what
+// vob_conv_state_update does), each thread for the channels it has just read.
+VOB_EXPORT int vob_causal_conv(const void* x, int code, long ld, int C, int taps, const float* w, const float* bias, float* cstate,
                                const int* positions, const int* row_seq, const int* seq_starts, const int* state_slots, int residual,
-                               int act, void* out, int out_code, long ld_out, int T, cudaStream_t stream) {
+                               int act, void* out, int out_code, long ld_out, int T, int single, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (C <= 0 || taps < 1 || !w || (taps > 1 && !cstate) || (act != 0 && act != 1) || (C + 127) / 128 > 65535) return VOB_ERR_BAD_ARG;
     const dim3 grid(T, (C + 127) / 128);
     const int vec = code == VOB_BF16 ? 8 : 4;
     const int out_vec = out_code == VOB_BF16 ? 8 : 4;
     const bool by16 = C % vec == 0 && ld % vec == 0 && (((uintptr_t)x) & 15) == 0 && ld_out % out_vec == 0 && (((uintptr_t)out) & 15) == 0 &&
-                      (((uintptr_t)w) & 15) == 0;
+                      (((uintptr_t)w) & 15) == 0 && (((uintptr_t)cstate) & 15) == 0;
 #define VOB_CONV(T_, TO_, V_)                                                                                                 \
     return by16 ? vob_launch(causal_conv_vec_kernel<T_, TO_, V_>, dim3(T, (C / V_ + 127) / 128), dim3(128), 0, stream, (const T_*)x, ld, C, \
-                             taps, w, bias, cstate, positions, row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out) \
+                             taps, w, bias, cstate, positions, row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out, single) \
                 : vob_launch(causal_conv_kernel<T_, TO_>, grid, dim3(128), 0, stream, (const T_*)x, ld, C, taps, w, bias, cstate,  \
-                             positions, row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out)
+                             positions, row_seq, seq_starts, state_slots, residual, act, (TO_*)out, ld_out, single)
     if (code == VOB_F32 && out_code == VOB_F32) VOB_CONV(float, float, 4);
     if (code == VOB_BF16 && out_code == VOB_BF16) VOB_CONV(__nv_bfloat16, __nv_bfloat16, 8);
     if (code == VOB_BF16 && out_code == VOB_F32) VOB_CONV(__nv_bfloat16, float, 8);

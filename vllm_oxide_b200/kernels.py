@@ -1113,12 +1113,13 @@ def conv_state_update(proj: torch.Tensor, x_off: int, conv_state: torch.Tensor, 
 @_timed
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], conv_state: Optional[torch.Tensor],
                 positions: torch.Tensor, row_seq: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, num_seqs: int,
-                out: torch.Tensor, residual: bool = False, act: str = "none") -> None:
+                out: torch.Tensor, residual: bool = False, act: str = "none", single: bool = False) -> None:
     """A short causal convolution over time on each channel: y[t, c] = bias[c] + sum_j weight[j, c] * x[t - taps + 1 + j, c]
     (weight float32 [taps, C]: tap by tap, the last row the current token's),
     inputs before the step's rows taken from `conv_state` (float32 [slots, taps - 1, C], the request's last inputs; zero at its
     start); out = act(y + x) with `residual`, act(y) without; act "none" or "silu". x [T, C] (a column range of a projection,
-    any row stride), out [T, C] in x's type or float32. The state is only read: `conv_state_update` moves it on afterwards."""
+    any row stride), out [T, C] in x's type or float32. The state is only read: `conv_state_update` moves it on afterwards;
+    with `single` (the caller knows that every request brings exactly one row) the kernel moves it on itself."""
     op = "causal_conv"
     _cuda(op, x, weight, bias, conv_state, positions, row_seq, seq_starts, state_slots, out)
     _rows_2d(x, op, "x")
@@ -1139,10 +1140,10 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     _int32_vec(row_seq, T, op, "row_seq")
     _int32_vec(seq_starts, num_seqs + 1, op, "seq_starts")
     _int32_vec(state_slots, num_seqs, op, "state_slots")
-    f = _fn("recurrence", "vob_causal_conv", [_P, _I, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _L, _I, _P])
+    f = _fn("recurrence", "vob_causal_conv", [_P, _I, _L, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _I, _L, _I, _I, _P])
     _check(f(_ptr(x), _code(x, op), x.stride(0), C, taps, _ptr(weight), _ptr(bias), _ptr(conv_state) if taps > 1 else _P(0),
              _ptr(positions), _ptr(row_seq), _ptr(seq_starts), _ptr(state_slots), 1 if residual else 0, 1 if act == "silu" else 0,
-             _ptr(out), _code(out, op), out.stride(0), T, _stream()), op)
+             _ptr(out), _code(out, op), out.stride(0), T, 1 if single else 0, _stream()), op)
 
 
 @_timed

@@ -276,9 +276,11 @@ class SandwichBlock:
         if canon is None:
             return h, None
         hc = ctx.alloc(h.shape)
+        # a step of single tokens: the convolution's kernel moves the state on itself
+        single = bool(ctx.decode_only and conv_state is not None)
         kernels.causal_conv(h, canon, None, conv_state, ctx.positions, ctx.row_seq, ctx.seq_starts, ctx.state_slots, ctx.seqs, hc,
-                            residual=True)
-        if conv_state is None:
+                            residual=True, single=single)
+        if conv_state is None or single:
             return hc, None
         if not TUNING.norm_tail:
             kernels.conv_state_update(h, 0, conv_state, ctx.seq_starts, ctx.state_slots, ctx.seqs)

@@ -328,9 +328,10 @@ class StateSpace(Mixer):
         T, inner, GN, C, H = x.shape[0], self.inner, self.GN, self.C, self.H
         proj = matmul(x, self.w_in, ctx.alloc((T, self.w_in.shape[0])))
         xbc = ctx.alloc((T, C), torch.float32)
+        single = bool(ctx.decode_only and conv_state is not None)      # single tokens: the kernel moves the state on itself
         kernels.causal_conv(proj[:, inner:inner + C], self.conv_w, self.conv_b, conv_state, ctx.positions, ctx.row_seq, ctx.seq_starts,
-                            ctx.state_slots, ctx.seqs, xbc, residual=False, act="silu")
-        if conv_state is not None:
+                            ctx.state_slots, ctx.seqs, xbc, residual=False, act="silu", single=single)
+        if conv_state is not None and not single:
             kernels.conv_state_update(proj, inner, conv_state, ctx.seq_starts, ctx.state_slots, ctx.seqs)
         dt, decay = ctx.alloc((T, H), torch.float32), ctx.alloc((T, H), torch.float32)
         kernels.ssm_steps(proj[:, inner + C:inner + C + H], self.dt_bias, self.a_log, dt, decay)
