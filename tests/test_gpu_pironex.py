@@ -588,6 +588,31 @@ def test_the_norm_behind_a_sub_layer_doing_more_on_its_way_changes_nothing(tmp_p
         assert _close(got[1][k], _plain_logits(d, reqs[k]), "float32"), k
 
 
+def test_the_shared_expert_beside_the_routed_ones_changes_nothing(tmp_path):
+    """`TUNING.moe_side_stream`: in steps of single tokens the shared expert runs on a second stream; the same bits, with
+    decode steps launched one by one and replayed from CUDA graphs."""
+    from vllm_oxide_b200.config import EngineConfig
+    from vllm_oxide_b200.engine import LLM, ModelRunner
+    from vllm_oxide_b200.sampling import SamplingParams
+    from vllm_oxide_b200.tuning import TUNING
+    d = _model_dir(tmp_path, "A")
+    prompts = [_tokens(n, 97, 60 + n) for n in (11, 4, 23)]
+    got = {}
+    before = TUNING.moe_side_stream
+    try:
+        for mode in (0, 1):
+            for graphs in (False, True):
+                TUNING.moe_side_stream = mode
+                eng = EngineConfig(max_batch_tokens=64, max_seqs=3, max_model_len=64, block_size=8, num_pages=24, dtype="bfloat16", cuda_graphs=graphs)
+                llm = LLM(ModelRunner.from_dir(d, eng))
+                got[(mode, graphs)] = [o.token_ids for o in llm.generate(prompts, SamplingParams(max_new_tokens=16, stop_token_ids=()))]
+                if graphs:
+                    assert llm.runner.decode_graphs and llm.runner._graphs
+    finally:
+        TUNING.moe_side_stream = before
+    assert got[(0, False)] == got[(1, False)] == got[(0, True)] == got[(1, True)]
+
+
 def test_the_stream_after_every_layer(tmp_path):
     """Layer by layer in float32: the stream that the engine's blocks hand on (the weighted sum over depth) equals the plain model's."""
     from vllm_oxide_b200.replay.trace import TraceSession

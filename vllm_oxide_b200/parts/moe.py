@@ -24,6 +24,7 @@ from typing import Sequence
 import torch
 
 from .. import kernels
+from ..tuning import TUNING
 from .base import FeedForward, StepContext, aligned
 from .linear import to_compute
 
@@ -58,6 +59,7 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"activation {activation!r} with limit {limit}: known are {', '.join(kernels.MOE_ACTIVATIONS)}, and the "
                              f"clamped one needs a positive limit")
         self.activation, self.limit = activation, float(limit)
+        self._side = None           # a second stream for the shared expert in steps of single tokens, made at first need
         self.shared = None
         if shared is not None:
             sg, su, sd, sgate, slimit = shared
@@ -92,10 +94,34 @@ class RoutedExperts(FeedForward):
             return ("moe",)
         return ("moe", "elementwise") + (("gemm_f32",) if dtype == torch.float32 else ("gemm_sm100",))
 
+    def _shared_expert(self, x, gu, hs, sh):
+        w_gu, w_down, fs, gated, slimit = self.shared
+        kernels.linear(x, w_gu, gu)
+        if self.activation == "clamped_swish":
+            kernels.glu_clamped(gu[:, :2 * fs], hs, slimit)
+        else:
+            kernels.glu(gu[:, :2 * fs], hs, "silu")
+        kernels.linear(hs, w_down, sh)
+
     def forward(self, x: torch.Tensor, ctx: StepContext, out=None) -> torch.Tensor:
         T = x.shape[0]
         P = T * self.top
         idx, w = ctx.alloc((T, self.top), torch.int32), ctx.alloc((T, self.top), torch.float32)
+        sh = sgate = side = None
+        if self.shared is not None:
+            w_gu, _, fs, gated, _ = self.shared
+            gu, hs, sh = ctx.alloc((T, w_gu.shape[0])), ctx.alloc((T, fs)), ctx.alloc((T, self.hidden))
+            sgate = gu[:, 2 * fs] if gated else None
+            if ctx.decode_only and TUNING.moe_side_stream:
+                # nothing of the shared expert depends on the routed ones: it runs beside them and joins before the sum
+                if self._side is None:
+                    self._side = torch.cuda.Stream(device=x.device)
+                side, main = self._side, torch.cuda.current_stream()
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    self._shared_expert(x, gu, hs, sh)
+            else:
+                self._shared_expert(x, gu, hs, sh)
         kernels.moe_route(x, self.w_router, ctx.positions, self.top, self.groups, self.keep, self.renorm, idx, w)
         large = x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
         tile = kernels.moe_tile_rows(P, self.E, self.hidden, self.ff, self.tensor_cores and large)
@@ -107,18 +133,7 @@ class RoutedExperts(FeedForward):
         y = ctx.alloc((P, self.hidden), torch.float32)
         kernels.moe_down(h, self.w_down, order, tile_expert, w, y, self.tensor_cores, tile)
         out = out if out is not None else ctx.alloc((T, self.hidden))
-        sh = sgate = None
-        if self.shared is not None:
-            w_gu, w_down, fs, gated, slimit = self.shared
-            gu = ctx.alloc((T, w_gu.shape[0]))
-            kernels.linear(x, w_gu, gu)
-            hs = ctx.alloc((T, fs))
-            if self.activation == "clamped_swish":
-                kernels.glu_clamped(gu[:, :2 * fs], hs, slimit)
-            else:
-                kernels.glu(gu[:, :2 * fs], hs, "silu")
-            sh = ctx.alloc((T, self.hidden))
-            kernels.linear(hs, w_down, sh)
-            sgate = gu[:, 2 * fs] if gated else None
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
         kernels.moe_combine(y, idx, out, sh, sgate)
         return out
